@@ -1,0 +1,72 @@
+"""ctypes bindings of the C ABI declared in include/alpha_moe_b200.h.
+
+The functions here take raw device addresses (ints) so that they can be driven from torch
+tensors (`t.data_ptr()`), cuda-python buffers or anything else; they are what the GPU parity
+tests call.
+"""
+from __future__ import annotations
+
+import ctypes
+import os
+
+_HERE = os.path.dirname(os.path.abspath(__file__))
+LIB_PATH = os.path.join(_HERE, "libalpha_moe_b200.so")
+
+if not os.path.exists(LIB_PATH):
+    raise ImportError(
+        f"{LIB_PATH} is missing: build it with `python -m alpha_moe_b200.build` "
+        "(the CUDA library is the only implementation; there is no fallback)")
+
+lib = ctypes.CDLL(LIB_PATH)
+
+_vp, _i, _f = ctypes.c_void_p, ctypes.c_int, ctypes.c_float
+
+lib.alpha_moe_b200_fused_moe_w8a8_up_down.restype = _i
+lib.alpha_moe_b200_fused_moe_w8a8_up_down.argtypes = [_vp] * 11 + [_i] * 10 + [_f, _vp]
+lib.alpha_moe_b200_read_status.restype = _i
+lib.alpha_moe_b200_read_status.argtypes = [ctypes.POINTER(ctypes.c_int32), _i]
+lib.alpha_moe_b200_plan.restype = _i
+lib.alpha_moe_b200_plan.argtypes = [_i, _i, _i, ctypes.POINTER(ctypes.c_int32)]
+lib.alpha_moe_b200_last_error.restype = ctypes.c_char_p
+lib.alpha_moe_b200_version.restype = ctypes.c_char_p
+
+
+class AlphaMoeError(RuntimeError):
+    pass
+
+
+def last_error() -> str:
+    return lib.alpha_moe_b200_last_error().decode()
+
+
+def _check(rc: int) -> None:
+    if rc != 0:
+        raise AlphaMoeError(f"alpha_moe_b200 error {rc}: {last_error()}")
+
+
+def fused_moe_w8a8_up_down(x, x_scale, w, w_scale, w2, w2_scale, out, sorted_token_ids, expert_ids,
+                           num_tokens_post_padded, topk_weights, top_k, M, K, N, num_experts, sorted_num,
+                           block_m, block_n, warp_n, stages, scaling_factor, stream=0) -> None:
+    """Raw call: every tensor argument is a device address (int)."""
+    _check(lib.alpha_moe_b200_fused_moe_w8a8_up_down(
+        x, x_scale, w, w_scale, w2, w2_scale, out, sorted_token_ids, expert_ids,
+        num_tokens_post_padded, topk_weights, top_k, M, K, N, num_experts, sorted_num,
+        block_m, block_n, warp_n, stages, scaling_factor, stream))
+
+
+def read_status(reset: bool = False):
+    """(code, block, where, iter) of the current device; code 0 = healthy.  Synchronises."""
+    buf = (ctypes.c_int32 * 4)()
+    _check(lib.alpha_moe_b200_read_status(buf, int(reset)))
+    return tuple(buf)
+
+
+def plan(K: int, block_m: int, stages: int):
+    """(ring_depth, padded_block_m, dynamic_smem_bytes) the launcher would use."""
+    buf = (ctypes.c_int32 * 3)()
+    _check(lib.alpha_moe_b200_plan(K, block_m, stages, buf))
+    return tuple(buf)
+
+
+def version() -> str:
+    return lib.alpha_moe_b200_version().decode()

@@ -1,0 +1,259 @@
+// Host side of the C ABI: argument checks, knob -> kernel variant, TMA descriptors, launch.
+//
+// Takes the place of the reference's launcher and its 160-way template dispatch
+// (csrc/kernels/fused_moe_w8a8/fused_moe_w8a8_up_down_acc.cu:1100-1303).  Differences that matter
+// to a caller: tensor maps are encoded once per (pointer, shape) and cached instead of per call
+// (:1135-1178), every CUDA / driver return code is checked and reported instead of exit()
+// (:14-21, :1143, :1167), and block_m only selects among four padded tile variants.
+#include <cuda.h>
+#include <cuda_runtime.h>
+
+#include <cstdarg>
+#include <cstdio>
+#include <cstring>
+#include <map>
+#include <mutex>
+#include <string>
+#include <tuple>
+
+#include "../../include/alpha_moe_b200.h"
+#include "fused_moe_kernel.cuh"
+
+namespace {
+
+thread_local std::string g_last_error;
+
+int fail(int code, const char* fmt, ...) {
+    char buf[512];
+    va_list ap;
+    va_start(ap, fmt);
+    vsnprintf(buf, sizeof(buf), fmt, ap);
+    va_end(ap);
+    g_last_error = buf;
+    return code;
+}
+
+#define CUDA_TRY(expr)                                                                             \
+    do {                                                                                           \
+        cudaError_t err__ = (expr);                                                                \
+        if (err__ != cudaSuccess)                                                                  \
+            return fail(ALPHA_MOE_E_CUDA, "%s failed: %s", #expr, cudaGetErrorString(err__));      \
+    } while (0)
+
+__device__ amoe::KernelStatus g_status;
+
+using EncodeTiledFn = CUresult (*)(CUtensorMap*, CUtensorMapDataType, cuuint32_t, void*, const cuuint64_t*,
+                                   const cuuint64_t*, const cuuint32_t*, const cuuint32_t*, CUtensorMapInterleave,
+                                   CUtensorMapSwizzle, CUtensorMapL2promotion, CUtensorMapFloatOOBfill);
+
+int get_encode_fn(EncodeTiledFn* out) {
+    static EncodeTiledFn fn = nullptr;
+    static std::mutex mu;
+    std::lock_guard<std::mutex> lock(mu);
+    if (!fn) {
+        void* p = nullptr;
+        cudaDriverEntryPointQueryResult qres;
+        CUDA_TRY(cudaGetDriverEntryPoint("cuTensorMapEncodeTiled", &p, cudaEnableDefault, &qres));
+        if (qres != cudaDriverEntryPointSuccess || !p)
+            return fail(ALPHA_MOE_E_CUDA, "cuTensorMapEncodeTiled is not available from this driver");
+        fn = reinterpret_cast<EncodeTiledFn>(p);
+    }
+    *out = fn;
+    return ALPHA_MOE_OK;
+}
+
+struct MapPair {
+    CUtensorMap w, w2;
+};
+using MapKey = std::tuple<int, const void*, const void*, int, int, int>;  // device, w, w2, E, N, K
+
+// Tensor maps depend only on the weight pointers and shapes, so a serving process encodes them
+// once per layer.  The cache is bounded; on overflow it is simply cleared.
+int get_maps(int device, const void* w, const void* w2, int E, int N, int K, const MapPair** out) {
+    static std::map<MapKey, MapPair> cache;
+    static std::mutex mu;
+    std::lock_guard<std::mutex> lock(mu);
+    MapKey key{device, w, w2, E, N, K};
+    auto it = cache.find(key);
+    if (it != cache.end()) {
+        *out = &it->second;
+        return ALPHA_MOE_OK;
+    }
+    EncodeTiledFn enc;
+    if (int rc = get_encode_fn(&enc)) return rc;
+    MapPair mp;
+    const cuuint64_t I = static_cast<cuuint64_t>(N) / 2, Kk = K, Nn = N;
+    {
+        // w [E][N][K] with gate/up interleaved in groups of 8 rows, seen as [E][I/8][2][8][K]
+        // (innermost first below).  One box = 16 groups x 1 half x 8 rows x 128 bytes = the 128 gate
+        // (or up) rows of one 128-column slice of the intermediate dimension, contiguous in shared memory.
+        cuuint64_t dims[5] = {Kk, 8, 2, I / 8, static_cast<cuuint64_t>(E)};
+        cuuint64_t strides[4] = {Kk, 8 * Kk, 16 * Kk, Nn * Kk};
+        cuuint32_t box[5] = {128, 8, 1, 16, 1};
+        cuuint32_t estr[5] = {1, 1, 1, 1, 1};
+        CUresult r = enc(&mp.w, CU_TENSOR_MAP_DATA_TYPE_UINT8, 5, const_cast<void*>(w), dims, strides, box, estr,
+                         CU_TENSOR_MAP_INTERLEAVE_NONE, CU_TENSOR_MAP_SWIZZLE_128B, CU_TENSOR_MAP_L2_PROMOTION_L2_256B,
+                         CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE);
+        if (r != CUDA_SUCCESS) return fail(ALPHA_MOE_E_CUDA, "cuTensorMapEncodeTiled(w) failed with CUresult %d", (int)r);
+    }
+    {
+        // w2 [E][K][I]: box = 128 hidden rows x 128 bytes of one intermediate slice; rows past K read zero.
+        cuuint64_t dims[3] = {I, Kk, static_cast<cuuint64_t>(E)};
+        cuuint64_t strides[2] = {I, Kk * I};
+        cuuint32_t box[3] = {128, 128, 1};
+        cuuint32_t estr[3] = {1, 1, 1};
+        CUresult r = enc(&mp.w2, CU_TENSOR_MAP_DATA_TYPE_UINT8, 3, const_cast<void*>(w2), dims, strides, box, estr,
+                         CU_TENSOR_MAP_INTERLEAVE_NONE, CU_TENSOR_MAP_SWIZZLE_128B, CU_TENSOR_MAP_L2_PROMOTION_L2_256B,
+                         CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE);
+        if (r != CUDA_SUCCESS) return fail(ALPHA_MOE_E_CUDA, "cuTensorMapEncodeTiled(w2) failed with CUresult %d", (int)r);
+    }
+    if (cache.size() > 4096) cache.clear();
+    auto ins = cache.emplace(key, mp);
+    *out = &ins.first->second;
+    return ALPHA_MOE_OK;
+}
+
+constexpr int kMaxDynSmem = 232448;  // 227 KB opt-in limit per CTA on sm_100
+
+int padded_block_m(int block_m) { return block_m <= 16 ? 16 : block_m <= 32 ? 32 : block_m <= 64 ? 64 : 128; }
+
+// Ring depth = the `stages` knob, lowered until the plan fits in shared memory.
+int plan(int K, int block_m, int stages, int* depth, int* bmp, int* smem_bytes) {
+    const int kc = K / 128;
+    const int b = padded_block_m(block_m);
+    int s = stages;
+    for (; s >= 1; --s) {
+        const int need = static_cast<int>(amoe::smem_plan(b, s, kc).total) + 1024;
+        if (need <= kMaxDynSmem) {
+            *depth = s;
+            *bmp = b;
+            *smem_bytes = need;
+            return ALPHA_MOE_OK;
+        }
+    }
+    return fail(ALPHA_MOE_E_ARG, "K=%d block_m=%d does not fit in shared memory even with one stage", K, block_m);
+}
+
+template <int BMP>
+int launch_variant(const CUtensorMap& mw, const CUtensorMap& mw2, const amoe::MoeParams& p, int grid, int smem_bytes,
+                   cudaStream_t stream) {
+    auto kern = amoe::fused_moe_w8a8_up_down_sm100_kernel<BMP>;
+    static int configured_smem[64] = {0};   // per device: largest dynamic smem size already opted in
+    int dev = 0;
+    CUDA_TRY(cudaGetDevice(&dev));
+    if (dev < 64 && configured_smem[dev] < smem_bytes) {
+        CUDA_TRY(cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, kMaxDynSmem));
+        configured_smem[dev] = kMaxDynSmem;
+    }
+    constexpr int threads = 128 * (BMP >= 64 ? 2 : 1) + 128;
+    kern<<<grid, threads, smem_bytes, stream>>>(mw, mw2, p);
+    CUDA_TRY(cudaGetLastError());
+    return ALPHA_MOE_OK;
+}
+
+}  // namespace
+
+extern "C" {
+
+int alpha_moe_b200_fused_moe_w8a8_up_down(const void* x, const float* x_scale, const void* w, const float* w_scale,
+                                          const void* w2, const float* w2_scale, void* out,
+                                          const int32_t* sorted_token_ids, const int32_t* expert_ids,
+                                          const int32_t* num_tokens_post_padded, const float* topk_weights, int top_k,
+                                          int M, int K, int N, int num_experts, int sorted_num, int block_m,
+                                          int block_n, int warp_n, int stages, float scaling_factor, void* stream) {
+    if (!x || !x_scale || !w || !w_scale || !w2 || !w2_scale || !out || !sorted_token_ids || !expert_ids ||
+        !num_tokens_post_padded || !topk_weights)
+        return fail(ALPHA_MOE_E_ARG, "null pointer argument");
+    if (M <= 0) return fail(ALPHA_MOE_E_ARG, "x must have at least one row (M=%d)", M);
+    if (K <= 0 || K % 128 != 0) return fail(ALPHA_MOE_E_ARG, "K dimension must be a multiple of 128 (K=%d)", K);
+    if (N <= 0 || N % 256 != 0) return fail(ALPHA_MOE_E_ARG, "N must be a multiple of 256 (N=%d)", N);
+    if (num_experts <= 0 || top_k <= 0 || sorted_num <= 0)
+        return fail(ALPHA_MOE_E_ARG, "num_experts, top_k and sorted_num must be positive");
+    if (!((block_n == 64 && warp_n == 4) || (block_n == 32 && warp_n == 8)))
+        return fail(ALPHA_MOE_E_ARG, "(block_n, warp_n) must be (64,4) or (32,8), got (%d,%d)", block_n, warp_n);
+    if (stages < 1 || stages > 5) return fail(ALPHA_MOE_E_ARG, "stages must be in 1..5, got %d", stages);
+    if (block_m < 8 || block_m > 128 || block_m % 8 != 0)
+        return fail(ALPHA_MOE_E_ARG, "block_m must be a multiple of 8 in 8..128, got %d", block_m);
+    if ((reinterpret_cast<uintptr_t>(w) | reinterpret_cast<uintptr_t>(w2) | reinterpret_cast<uintptr_t>(x)) & 15)
+        return fail(ALPHA_MOE_E_ARG, "x, w and w2 must be 16-byte aligned");
+    if (reinterpret_cast<uintptr_t>(out) & 3) return fail(ALPHA_MOE_E_ARG, "out must be 4-byte aligned");
+    if (static_cast<long long>(M) * top_k > 0x7FFFFFFFLL) return fail(ALPHA_MOE_E_ARG, "M*top_k overflows int32");
+
+    int depth, bmp, smem_bytes;
+    if (int rc = plan(K, block_m, stages, &depth, &bmp, &smem_bytes)) return rc;
+
+    int dev = 0;
+    CUDA_TRY(cudaGetDevice(&dev));
+    const MapPair* maps = nullptr;
+    if (int rc = get_maps(dev, w, w2, num_experts, N, K, &maps)) return rc;
+
+    amoe::KernelStatus* status = nullptr;
+    CUDA_TRY(cudaGetSymbolAddress(reinterpret_cast<void**>(&status), g_status));
+
+    amoe::MoeParams p;
+    p.x = static_cast<const uint8_t*>(x);
+    p.x_scale = x_scale;
+    p.w_scale = w_scale;
+    p.w2_scale = w2_scale;
+    p.out = static_cast<__nv_bfloat16*>(out);
+    p.sorted_token_ids = sorted_token_ids;
+    p.expert_ids = expert_ids;
+    p.num_tokens_post_padded = num_tokens_post_padded;
+    p.topk_weights = topk_weights;
+    p.top_k = top_k;
+    p.M = M;
+    p.K = K;
+    p.N = N;
+    p.E = num_experts;
+    p.sorted_num = sorted_num;
+    p.block_m = block_m;
+    p.stages = depth;
+    p.lag = depth - 1 < 2 ? depth - 1 : 2;
+    p.scaling = scaling_factor;
+    p.status = status;
+
+    const long long nblocks = (static_cast<long long>(sorted_num) + block_m - 1) / block_m;
+    const long long grid = nblocks * (N / 256);
+    if (grid > 0x7FFFFFFFLL) return fail(ALPHA_MOE_E_ARG, "grid too large");
+    cudaStream_t st = static_cast<cudaStream_t>(stream);
+    switch (bmp) {
+        case 16: return launch_variant<16>(maps->w, maps->w2, p, static_cast<int>(grid), smem_bytes, st);
+        case 32: return launch_variant<32>(maps->w, maps->w2, p, static_cast<int>(grid), smem_bytes, st);
+        case 64: return launch_variant<64>(maps->w, maps->w2, p, static_cast<int>(grid), smem_bytes, st);
+        default: return launch_variant<128>(maps->w, maps->w2, p, static_cast<int>(grid), smem_bytes, st);
+    }
+}
+
+int alpha_moe_b200_read_status(int32_t* out4, int reset) {
+    if (!out4) return fail(ALPHA_MOE_E_ARG, "out4 is null");
+    CUDA_TRY(cudaDeviceSynchronize());
+    amoe::KernelStatus h;
+    CUDA_TRY(cudaMemcpyFromSymbol(&h, g_status, sizeof(h)));
+    out4[0] = h.code;
+    out4[1] = h.block;
+    out4[2] = h.where;
+    out4[3] = h.iter;
+    if (reset) {
+        amoe::KernelStatus z = {0, 0, 0, 0};
+        CUDA_TRY(cudaMemcpyToSymbol(g_status, &z, sizeof(z)));
+    }
+    return ALPHA_MOE_OK;
+}
+
+int alpha_moe_b200_plan(int K, int block_m, int stages, int32_t* out3) {
+    if (!out3) return fail(ALPHA_MOE_E_ARG, "out3 is null");
+    if (K <= 0 || K % 128 != 0) return fail(ALPHA_MOE_E_ARG, "K dimension must be a multiple of 128 (K=%d)", K);
+    if (block_m < 8 || block_m > 128 || block_m % 8 != 0) return fail(ALPHA_MOE_E_ARG, "bad block_m %d", block_m);
+    if (stages < 1 || stages > 5) return fail(ALPHA_MOE_E_ARG, "stages must be in 1..5, got %d", stages);
+    int depth, bmp, smem_bytes;
+    if (int rc = plan(K, block_m, stages, &depth, &bmp, &smem_bytes)) return rc;
+    out3[0] = depth;
+    out3[1] = bmp;
+    out3[2] = smem_bytes;
+    return ALPHA_MOE_OK;
+}
+
+const char* alpha_moe_b200_last_error(void) { return g_last_error.c_str(); }
+const char* alpha_moe_b200_version(void) { return "alpha_moe_b200 0.1 (sm_100a)"; }
+
+}  // extern "C"

@@ -1,0 +1,58 @@
+/* C ABI of the B200 (sm_100a) fused W8A8 MoE library, libalpha_moe_b200.so.
+ *
+ * Every entry point takes plain device pointers and sizes - no torch types - and returns 0 on
+ * success or a negative ALPHA_MOE_E_* code; alpha_moe_b200_last_error() then gives the message
+ * of the failing call on the calling thread.  Nothing here allocates device memory unless the
+ * comment of the entry point says so.  All work is enqueued on `stream` (a cudaStream_t passed
+ * as void*, NULL = default stream) and is asynchronous with respect to the host.
+ *
+ * Citations are into the reference project (Aleph-Alpha/Alpha-MoE).
+ */
+#ifndef ALPHA_MOE_B200_H_
+#define ALPHA_MOE_B200_H_
+
+#include <stdint.h>
+
+#ifdef __cplusplus
+extern "C" {
+#endif
+
+#define ALPHA_MOE_OK 0
+#define ALPHA_MOE_E_ARG (-1)     /* argument rejected (shape, knob, alignment, null pointer) */
+#define ALPHA_MOE_E_CUDA (-2)    /* a CUDA runtime / driver call failed */
+#define ALPHA_MOE_E_DEVICE (-3)  /* the kernel reported a run-out wait through its status word */
+
+/* Replaces: void fused_moe_w8a8_wgmma_up_down_acc(...) declared at csrc/torch_interface.cpp:12-34 and
+ * defined at csrc/kernels/fused_moe_w8a8/fused_moe_w8a8_up_down_acc.cu:1258-1303 (the launcher the
+ * torch operator calls).  Same arguments in the same order and meaning:
+ *   x [M,K] fp8 e4m3, x_scale [M,K/128] f32, w [E,N,K] fp8 (gate/up rows interleaved by 8),
+ *   w_scale [E,N/128,K/128] f32 (interleaved by 1), w2 [E,K,N/2] fp8, w2_scale [E,K/128,N/256] f32,
+ *   out [M,K] bf16 - must be zero on entry, results are accumulated in place,
+ *   sorted_token_ids [sorted_num] i32, expert_ids [ceil(sorted_num/block_m)] i32,
+ *   num_tokens_post_padded [1] i32, topk_weights [M,top_k] f32.
+ * block_m is semantic (the block size given to moe_align_block_size); block_n/warp_n/stages are the
+ * reference's tuning knobs and are validated like csrc/torch_interface.cpp:62-64:
+ * (block_n,warp_n) in {(64,4),(32,8)}, 1 <= stages <= 5, block_m in {8,16,...,128}.
+ * Requires K % 128 == 0, N % 256 == 0, 16-byte aligned w / w2 / x. */
+int alpha_moe_b200_fused_moe_w8a8_up_down(
+    const void* x, const float* x_scale, const void* w, const float* w_scale, const void* w2,
+    const float* w2_scale, void* out, const int32_t* sorted_token_ids, const int32_t* expert_ids,
+    const int32_t* num_tokens_post_padded, const float* topk_weights, int top_k, int M, int K, int N,
+    int num_experts, int sorted_num, int block_m, int block_n, int warp_n, int stages,
+    float scaling_factor, void* stream);
+
+/* Reads (and optionally clears) the status word of the current device: out4 = {code, block, where, iter};
+ * code 0 means no kernel wait has ever run out.  Synchronises the device. */
+int alpha_moe_b200_read_status(int32_t* out4, int reset);
+
+/* Ring depth, padded block_m and dynamic shared memory the launcher would use; for tuners and tests.
+ * out3 = {ring_depth, padded_block_m, dynamic_smem_bytes}.  No device work. */
+int alpha_moe_b200_plan(int K, int block_m, int stages, int32_t* out3);
+
+const char* alpha_moe_b200_last_error(void);
+const char* alpha_moe_b200_version(void);
+
+#ifdef __cplusplus
+}
+#endif
+#endif /* ALPHA_MOE_B200_H_ */
