@@ -41,6 +41,10 @@ int fail(int code, const char* fmt, ...) {
     } while (0)
 
 __device__ amoe::KernelStatus g_status;
+#ifdef AMOE_TRACE
+long long* g_trace = nullptr;
+int g_trace_block = 0;
+#endif
 
 using EncodeTiledFn = CUresult (*)(CUtensorMap*, CUtensorMapDataType, cuuint32_t, void*, const cuuint64_t*,
                                    const cuuint64_t*, const cuuint32_t*, const cuuint32_t*, CUtensorMapInterleave,
@@ -84,23 +88,21 @@ int get_maps(int device, const void* w, const void* w2, int E, int N, int K, con
     MapPair mp;
     const cuuint64_t I = static_cast<cuuint64_t>(N) / 2, Kk = K, Nn = N;
     {
-        // w [E][N][K] with gate/up interleaved in groups of 8 rows, seen as [E][I/8][2][8][K]
-        // (innermost first below).  One box = 16 groups x 1 half x 8 rows x 128 bytes = the 128 gate
-        // (or up) rows of one 128-column slice of the intermediate dimension, contiguous in shared memory.
-        cuuint64_t dims[5] = {Kk, 8, 2, I / 8, static_cast<cuuint64_t>(E)};
-        cuuint64_t strides[4] = {Kk, 8 * Kk, 16 * Kk, Nn * Kk};
-        cuuint32_t box[5] = {128, 8, 1, 16, 1};
-        cuuint32_t estr[5] = {1, 1, 1, 1, 1};
-        CUresult r = enc(&mp.w, CU_TENSOR_MAP_DATA_TYPE_UINT8, 5, const_cast<void*>(w), dims, strides, box, estr,
+        // w [E][N][K]: box = 256 consecutive (interleaved) rows x 128 bytes of K.
+        cuuint64_t dims[3] = {Kk, Nn, static_cast<cuuint64_t>(E)};
+        cuuint64_t strides[2] = {Kk, Nn * Kk};
+        cuuint32_t box[3] = {128, 256, 1};
+        cuuint32_t estr[3] = {1, 1, 1};
+        CUresult r = enc(&mp.w, CU_TENSOR_MAP_DATA_TYPE_UINT8, 3, const_cast<void*>(w), dims, strides, box, estr,
                          CU_TENSOR_MAP_INTERLEAVE_NONE, CU_TENSOR_MAP_SWIZZLE_128B, CU_TENSOR_MAP_L2_PROMOTION_L2_256B,
                          CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE);
         if (r != CUDA_SUCCESS) return fail(ALPHA_MOE_E_CUDA, "cuTensorMapEncodeTiled(w) failed with CUresult %d", (int)r);
     }
     {
-        // w2 [E][K][I]: box = 128 hidden rows x 128 bytes of one intermediate slice; rows past K read zero.
+        // w2 [E][K][I]: box = 256 hidden rows x 128 bytes of one intermediate slice; rows past K read zero.
         cuuint64_t dims[3] = {I, Kk, static_cast<cuuint64_t>(E)};
         cuuint64_t strides[2] = {I, Kk * I};
-        cuuint32_t box[3] = {128, 128, 1};
+        cuuint32_t box[3] = {128, 256, 1};
         cuuint32_t estr[3] = {1, 1, 1};
         CUresult r = enc(&mp.w2, CU_TENSOR_MAP_DATA_TYPE_UINT8, 3, const_cast<void*>(w2), dims, strides, box, estr,
                          CU_TENSOR_MAP_INTERLEAVE_NONE, CU_TENSOR_MAP_SWIZZLE_128B, CU_TENSOR_MAP_L2_PROMOTION_L2_256B,
@@ -211,6 +213,10 @@ int alpha_moe_b200_fused_moe_w8a8_up_down(const void* x, const float* x_scale, c
     p.lag = depth - 1 < 2 ? depth - 1 : 2;
     p.scaling = scaling_factor;
     p.status = status;
+#ifdef AMOE_TRACE
+    p.trace = g_trace;
+    p.trace_block = g_trace_block;
+#endif
 
     const long long nblocks = (static_cast<long long>(sorted_num) + block_m - 1) / block_m;
     const long long grid = nblocks * (N / 256);
@@ -252,6 +258,13 @@ int alpha_moe_b200_plan(int K, int block_m, int stages, int32_t* out3) {
     out3[2] = smem_bytes;
     return ALPHA_MOE_OK;
 }
+
+#ifdef AMOE_TRACE
+void alpha_moe_b200_debug_set_trace(long long* buf, int block) {
+    g_trace = buf;
+    g_trace_block = block;
+}
+#endif
 
 const char* alpha_moe_b200_last_error(void) { return g_last_error.c_str(); }
 const char* alpha_moe_b200_version(void) { return "alpha_moe_b200 0.1 (sm_100a)"; }

@@ -41,6 +41,12 @@ __device__ __forceinline__ void fence_mbar_init() {
 __device__ __forceinline__ void mbar_arrive(uint64_t* bar) {
     asm volatile("mbarrier.arrive.shared::cta.b64 _, [%0];" ::"r"(smem_u32(bar)) : "memory");
 }
+// Arrival without release ordering: for hand-offs where the arriving thread has written nothing the
+// waiter will read (e.g. "TMEM has been read", "ring slot is free").  A default (release) arrive would
+// also wait for this thread's outstanding global reductions to be acknowledged by L2.
+__device__ __forceinline__ void mbar_arrive_relaxed(uint64_t* bar) {
+    asm volatile("mbarrier.arrive.relaxed.cta.shared::cta.b64 _, [%0];" ::"r"(smem_u32(bar)) : "memory");
+}
 __device__ __forceinline__ void mbar_arrive_expect_tx(uint64_t* bar, uint32_t bytes) {
     asm volatile("mbarrier.arrive.expect_tx.shared::cta.b64 _, [%0], %1;" ::"r"(smem_u32(bar)), "r"(bytes)
                  : "memory");
@@ -92,15 +98,6 @@ __device__ __forceinline__ void fence_proxy_async_smem() {
 __device__ __forceinline__ void prefetch_tmap(const CUtensorMap* m) {
     asm volatile("prefetch.tensormap [%0];" ::"l"(reinterpret_cast<uint64_t>(m)) : "memory");
 }
-__device__ __forceinline__ void tma_load_5d(void* dst, const CUtensorMap* m, uint64_t* bar, int c0, int c1, int c2,
-                                            int c3, int c4) {
-    asm volatile(
-        "cp.async.bulk.tensor.5d.shared::cluster.global.tile.mbarrier::complete_tx::bytes"
-        " [%0], [%1, {%3, %4, %5, %6, %7}], [%2];"
-        ::"r"(smem_u32(dst)), "l"(reinterpret_cast<uint64_t>(m)), "r"(smem_u32(bar)), "r"(c0), "r"(c1), "r"(c2),
-        "r"(c3), "r"(c4)
-        : "memory");
-}
 __device__ __forceinline__ void tma_load_3d(void* dst, const CUtensorMap* m, uint64_t* bar, int c0, int c1, int c2) {
     asm volatile(
         "cp.async.bulk.tensor.3d.shared::cluster.global.tile.mbarrier::complete_tx::bytes"
@@ -136,12 +133,15 @@ __device__ __forceinline__ void tc_fence_before() { asm volatile("tcgen05.fence:
 __device__ __forceinline__ void tc_fence_after() { asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory"); }
 
 // Shared-memory matrix descriptor, K-major operand stored as rows of 128 bytes with the 128-byte
-// swizzle (what TMA writes with CU_TENSOR_MAP_SWIZZLE_128B): 8-row groups are 1024 B apart (SBO),
-// the leading offset is unused for this layout, descriptor version 1, layout type 2.
-__device__ __forceinline__ uint64_t umma_desc_sw128(uint32_t smem_addr) {
+// swizzle (what TMA writes with CU_TENSOR_MAP_SWIZZLE_128B); the leading offset is unused for this
+// layout, descriptor version 1, layout type 2.
+// `sbo` is the distance between consecutive 8-row groups of the operand: 1024 for a dense tile, 2048
+// to take every other 8-row group of a tile (how the gate / up halves of the interleaved `w` rows are
+// picked apart without moving any data).
+__device__ __forceinline__ uint64_t umma_desc_sw128(uint32_t smem_addr, uint32_t sbo = 1024u) {
     uint64_t d = 0;
     d |= static_cast<uint64_t>((smem_addr & 0x3FFFFu) >> 4);        // start address  [0,14)
-    d |= static_cast<uint64_t>(1024u >> 4) << 32;                   // stride byte offset [32,46)
+    d |= static_cast<uint64_t>(sbo >> 4) << 32;                     // stride byte offset [32,46)
     d |= static_cast<uint64_t>(1) << 46;                            // version [46,48)
     d |= static_cast<uint64_t>(2) << 61;                            // SWIZZLE_128B [61,64)
     return d;
@@ -149,6 +149,44 @@ __device__ __forceinline__ uint64_t umma_desc_sw128(uint32_t smem_addr) {
 // Instruction descriptor for kind::f8f6f4, e4m3 x e4m3 -> f32, both operands K-major.
 __host__ __device__ constexpr uint32_t umma_idesc_e4m3(uint32_t m, uint32_t n) {
     return (1u << 4) | ((n >> 3) << 17) | ((m >> 4) << 24);
+}
+// One 128-deep K chunk (four K=32 steps) of two independent accumulators that share the B operand:
+//   D0 = A0 * B, D1 = A1 * B   (fresh accumulation: the first step overwrites D).
+// All eight instructions sit in one asm block so that the issuing thread spends no instructions
+// between them; descriptors advance by 32 bytes (2 in units of 16 B) per K step.
+__device__ __forceinline__ void umma_f8_chunk2(uint32_t d0, uint32_t d1, uint64_t a0, uint64_t a1, uint64_t b,
+                                               uint32_t idesc) {
+    asm volatile(
+        "{\n\t.reg .pred pf, pt;\n\t.reg .b64 a0k, a1k, bk;\n\t"
+        "setp.ne.b32 pf, 0, 0;\n\tsetp.eq.b32 pt, 0, 0;\n\t"
+        "tcgen05.mma.cta_group::1.kind::f8f6f4 [%0], %2, %4, %5, pf;\n\t"
+        "tcgen05.mma.cta_group::1.kind::f8f6f4 [%1], %3, %4, %5, pf;\n\t"
+        "add.u64 a0k, %2, 2;\n\tadd.u64 a1k, %3, 2;\n\tadd.u64 bk, %4, 2;\n\t"
+        "tcgen05.mma.cta_group::1.kind::f8f6f4 [%0], a0k, bk, %5, pt;\n\t"
+        "tcgen05.mma.cta_group::1.kind::f8f6f4 [%1], a1k, bk, %5, pt;\n\t"
+        "add.u64 a0k, %2, 4;\n\tadd.u64 a1k, %3, 4;\n\tadd.u64 bk, %4, 4;\n\t"
+        "tcgen05.mma.cta_group::1.kind::f8f6f4 [%0], a0k, bk, %5, pt;\n\t"
+        "tcgen05.mma.cta_group::1.kind::f8f6f4 [%1], a1k, bk, %5, pt;\n\t"
+        "add.u64 a0k, %2, 6;\n\tadd.u64 a1k, %3, 6;\n\tadd.u64 bk, %4, 6;\n\t"
+        "tcgen05.mma.cta_group::1.kind::f8f6f4 [%0], a0k, bk, %5, pt;\n\t"
+        "tcgen05.mma.cta_group::1.kind::f8f6f4 [%1], a1k, bk, %5, pt;\n\t}"
+        ::"r"(d0), "r"(d1), "l"(a0), "l"(a1), "l"(b), "r"(idesc)
+        : "memory");
+}
+// Same for a single accumulator.
+__device__ __forceinline__ void umma_f8_chunk1(uint32_t d0, uint64_t a0, uint64_t b, uint32_t idesc) {
+    asm volatile(
+        "{\n\t.reg .pred pf, pt;\n\t.reg .b64 a0k, bk;\n\t"
+        "setp.ne.b32 pf, 0, 0;\n\tsetp.eq.b32 pt, 0, 0;\n\t"
+        "tcgen05.mma.cta_group::1.kind::f8f6f4 [%0], %1, %2, %3, pf;\n\t"
+        "add.u64 a0k, %1, 2;\n\tadd.u64 bk, %2, 2;\n\t"
+        "tcgen05.mma.cta_group::1.kind::f8f6f4 [%0], a0k, bk, %3, pt;\n\t"
+        "add.u64 a0k, %1, 4;\n\tadd.u64 bk, %2, 4;\n\t"
+        "tcgen05.mma.cta_group::1.kind::f8f6f4 [%0], a0k, bk, %3, pt;\n\t"
+        "add.u64 a0k, %1, 6;\n\tadd.u64 bk, %2, 6;\n\t"
+        "tcgen05.mma.cta_group::1.kind::f8f6f4 [%0], a0k, bk, %3, pt;\n\t}"
+        ::"r"(d0), "l"(a0), "l"(b), "r"(idesc)
+        : "memory");
 }
 // D[tmem] (+)= A[smem] * B[smem]; issued by one thread.
 __device__ __forceinline__ void umma_f8(uint32_t d_tmem, uint64_t a_desc, uint64_t b_desc, uint32_t idesc,
@@ -183,7 +221,26 @@ __device__ __forceinline__ void named_bar_sync(int id, int nthreads) {
 }
 __device__ __forceinline__ void red_add_bf16x2(__nv_bfloat16* addr, float lo, float hi) {
     __nv_bfloat162 v = __floats2bfloat162_rn(lo, hi);
-    asm volatile("red.global.add.noftz.bf16x2 [%0], %1;" ::"l"(addr), "r"(*reinterpret_cast<uint32_t*>(&v)) : "memory");
+    // no "memory" clobber: nothing in a kernel reads `out` back, and the clobber would serialise the
+    // shared-memory loads of neighbouring iterations behind each reduction
+    asm volatile("red.global.add.noftz.bf16x2 [%0], %1;" ::"l"(addr), "r"(*reinterpret_cast<uint32_t*>(&v)));
+}
+// Same, issued only where `row < nrows` (no branch: the bound check is a predicate on the instruction).
+__device__ __forceinline__ void red_add_bf16x2_if(__nv_bfloat16* addr, float lo, float hi, int row, int nrows) {
+    __nv_bfloat162 v = __floats2bfloat162_rn(lo, hi);
+    asm volatile(
+        "{\n\t.reg .pred p;\n\tsetp.lt.s32 p, %2, %3;\n\t"
+        "@p red.global.add.noftz.bf16x2 [%0], %1;\n\t}"
+        ::"l"(addr), "r"(*reinterpret_cast<uint32_t*>(&v)), "r"(row), "r"(nrows));
+}
+// Register re-balancing between warpgroups (all four warps of a warpgroup must execute it).
+template <int N>
+__device__ __forceinline__ void setmaxnreg_inc() {
+    asm volatile("setmaxnreg.inc.sync.aligned.u32 %0;" ::"n"(N));
+}
+template <int N>
+__device__ __forceinline__ void setmaxnreg_dec() {
+    asm volatile("setmaxnreg.dec.sync.aligned.u32 %0;" ::"n"(N));
 }
 __device__ __forceinline__ float bf16_round(float v) { return __bfloat162float(__float2bfloat16_rn(v)); }
 
