@@ -1,0 +1,127 @@
+"""CPU tests of the host side: layout / table helpers against reference goldens, the C ABI
+library (loads, exports every declared symbol, argument validation without touching a GPU)."""
+import ctypes
+import json
+import os
+import re
+
+import numpy as np
+import pytest
+import torch
+
+ROOT = os.path.dirname(os.path.dirname(os.path.abspath(__file__)))
+GOLD = os.path.join(os.path.dirname(__file__), "golden")
+
+
+def test_interleave_tensor_matches_reference_goldens():
+    from alpha_moe_python.utils import interleave_tensor
+    g = np.load(os.path.join(GOLD, "ref_interleave.npz"))
+    for src, rep, key in (("a", 8, "a_rep8"), ("a", 2, "a_rep2"), ("b", 8, "b_rep8"), ("s", 1, "s_rep1")):
+        got = interleave_tensor(torch.from_numpy(g[src]), rep)
+        assert got.is_contiguous()
+        assert torch.equal(got, torch.from_numpy(g[key]))
+    with pytest.raises(ValueError):
+        interleave_tensor(torch.zeros(1, 24, 2), 8)
+
+
+def test_get_best_config_matches_reference_goldens():
+    from alpha_moe_python.utils import get_best_config
+    with open(os.path.join(GOLD, "ref_best_config.json")) as f:
+        want = json.load(f)
+    table = os.path.join(GOLD, "best_config_table.json")
+    for q, knobs in want.items():
+        assert get_best_config(table, int(q)) == knobs
+
+
+def test_shipped_config_tables_are_valid():
+    cfg_dir = os.path.join(ROOT, "configs")
+    if not os.path.isdir(cfg_dir):
+        pytest.skip("no tuned tables shipped")
+    for name in os.listdir(cfg_dir):
+        if not name.endswith(".json"):
+            continue
+        with open(os.path.join(cfg_dir, name)) as f:
+            table = json.load(f)
+        assert table
+        for bucket, knobs in table.items():
+            assert int(bucket) > 0
+            assert knobs["block_m"] % 8 == 0 and 8 <= knobs["block_m"] <= 128
+            assert (knobs["block_n"], knobs["warp_n"]) in ((64, 4), (32, 8))
+            assert 1 <= knobs["stages"] <= 5
+
+
+def _declared_symbols():
+    names = []
+    inc = os.path.join(ROOT, "include")
+    for fn in os.listdir(inc):
+        if fn.endswith(".h"):
+            text = open(os.path.join(inc, fn)).read()
+            text = re.sub(r"/\*.*?\*/", "", text, flags=re.S)
+            names += re.findall(r"\b(alpha_moe_b200_\w+)\s*\(", text)
+    return sorted(set(names))
+
+
+def test_capi_library_exports_every_declared_symbol():
+    from alpha_moe_b200 import capi
+    names = _declared_symbols()
+    assert "alpha_moe_b200_fused_moe_w8a8_up_down" in names
+    for n in names:
+        assert hasattr(capi.lib, n), f"{n} declared in include/ but not exported"
+    assert "sm_100a" in capi.version()
+
+
+def test_capi_rejects_bad_arguments_without_a_gpu():
+    from alpha_moe_b200 import capi
+    p = 0x1000   # never dereferenced: validation fails first
+    base = dict(x=p, x_scale=p, w=p, w_scale=p, w2=p, w2_scale=p, out=p, sorted_token_ids=p, expert_ids=p,
+                num_tokens_post_padded=p, topk_weights=p, top_k=2, M=4, K=512, N=256, num_experts=8,
+                sorted_num=128, block_m=16, block_n=32, warp_n=8, stages=3, scaling_factor=1.0)
+
+    def call(**kw):
+        a = dict(base, **kw)
+        return capi.fused_moe_w8a8_up_down(*a.values())
+
+    for bad, msg in ((dict(K=500), "multiple of 128"), (dict(block_n=64, warp_n=8), "block_n"),
+                     (dict(stages=0), "stages"), (dict(stages=6), "stages"), (dict(block_m=12), "block_m"),
+                     (dict(block_m=136), "block_m"), (dict(N=384), "multiple of 256"), (dict(M=0), "at least one row"),
+                     (dict(x=0), "null"), (dict(w=p + 8), "aligned")):
+        with pytest.raises(capi.AlphaMoeError, match=msg):
+            call(**bad)
+
+
+def test_plan_fits_shared_memory_for_every_knob():
+    from alpha_moe_b200 import capi
+    for k in (128, 2048, 4096, 7168):
+        for bm in range(8, 129, 8):
+            for st in range(1, 6):
+                depth, bmp, smem = capi.plan(k, bm, st)
+                assert 1 <= depth <= st and bmp >= bm and bmp in (16, 32, 64, 128)
+                assert smem <= 232448
+    assert capi.plan(7168, 16, 5)[0] == 5
+
+
+def test_torch_operator_schema_is_the_reference_schema():
+    import alpha_moe  # noqa: F401
+    schema = str(torch.ops.alpha_moe.fused_moe_w8a8_up_down.default._schema)
+    want = ("alpha_moe::fused_moe_w8a8_up_down(Tensor x, Tensor x_scale, Tensor w, Tensor w_scale, Tensor w2, "
+            "Tensor w2_scale, Tensor sorted_token_ids, Tensor expert_ids, Tensor num_tokens_post_padded, "
+            "Tensor topk_weights, Tensor(a!) out, int top_k, int block_m, int block_n, int warp_n, int stages, "
+            "float scaling_factor) -> ()")
+    assert schema == want
+    # CUDA-only: calling it with CPU tensors must fail, never fall back
+    x = torch.zeros(2, 128, dtype=torch.float8_e4m3fn)
+    with pytest.raises((RuntimeError, NotImplementedError)):
+        torch.ops.alpha_moe.fused_moe_w8a8_up_down(
+            x, torch.zeros(2, 1), torch.zeros(1, 256, 128, dtype=torch.float8_e4m3fn), torch.zeros(1, 2, 1),
+            torch.zeros(1, 128, 128, dtype=torch.float8_e4m3fn), torch.zeros(1, 1, 1),
+            torch.zeros(32, dtype=torch.int32), torch.zeros(2, dtype=torch.int32), torch.zeros(1, dtype=torch.int32),
+            torch.zeros(2, 1), torch.zeros(2, 128, dtype=torch.bfloat16), 1, 16, 32, 8, 3, 1.0)
+
+
+def test_no_product_module_imports_the_oracle():
+    pkg = os.path.join(ROOT, "alpha_moe_b200")
+    for dirpath, _, files in os.walk(pkg):
+        for fn in files:
+            if fn.endswith((".py", ".cu", ".cuh", ".cpp", ".h")):
+                text = open(os.path.join(dirpath, fn)).read()
+                assert "oracle" not in text.replace("# oracle", ""), f"{fn} mentions the oracle"
