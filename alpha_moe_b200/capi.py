@@ -26,7 +26,7 @@ lib.alpha_moe_b200_fused_moe_w8a8_up_down.argtypes = [_vp] * 11 + [_i] * 10 + [_
 lib.alpha_moe_b200_read_status.restype = _i
 lib.alpha_moe_b200_read_status.argtypes = [ctypes.POINTER(ctypes.c_int32), _i]
 lib.alpha_moe_b200_plan.restype = _i
-lib.alpha_moe_b200_plan.argtypes = [_i, _i, _i, ctypes.POINTER(ctypes.c_int32)]
+lib.alpha_moe_b200_plan.argtypes = [_i, _i, _i, _i, ctypes.POINTER(ctypes.c_int32)]
 lib.alpha_moe_b200_last_error.restype = ctypes.c_char_p
 lib.alpha_moe_b200_version.restype = ctypes.c_char_p
 
@@ -61,10 +61,10 @@ def read_status(reset: bool = False):
     return tuple(buf)
 
 
-def plan(K: int, block_m: int, stages: int):
-    """(ring_depth, padded_block_m, dynamic_smem_bytes) the launcher would use."""
-    buf = (ctypes.c_int32 * 3)()
-    _check(lib.alpha_moe_b200_plan(K, block_m, stages, buf))
+def plan(K: int, block_m: int, stages: int, block_n: int = 32):
+    """(ring_depth, padded_block_m, dynamic_smem_bytes, slices_per_cta) the launcher would use."""
+    buf = (ctypes.c_int32 * 4)()
+    _check(lib.alpha_moe_b200_plan(K, block_m, block_n, stages, buf))
     return tuple(buf)
 
 

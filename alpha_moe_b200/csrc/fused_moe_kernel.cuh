@@ -2,9 +2,10 @@
 // down-projection -> weighted accumulation into `out`, one launch per layer call.
 //
 // Replaces csrc/kernels/fused_moe_w8a8/fused_moe_w8a8_up_down_acc.cu:654-1098 (the Hopper
-// wgmma megakernel).  Same decomposition of the problem - one CTA per (block of block_m sorted
-// assignments of one expert, 128-wide slice of the intermediate dimension) - but a different
-// machine mapping:
+// wgmma megakernel).  One CTA handles one block of block_m sorted assignments of one expert and
+// SPC (1 or 2) 128-wide slices of the intermediate dimension - SPC = 1 is the reference's
+// decomposition (:1125); SPC = 2 lets one CTA own two slices so that each (token, expert) pair adds
+// into `out` once instead of twice.  The machine mapping is new:
 //   * weights are the UMMA "M" operand (128 rows per instruction), the gathered tokens the "N"
 //     operand, accumulators live in TMEM (tcgen05.mma kind::f8f6f4), not in registers;
 //   * the gate and up halves of the 8-row-interleaved `w` are separated for free: one TMA box
@@ -15,12 +16,15 @@
 //     registers with the (128x128 weight block) x (token, 128-group) scales (reference :915-933
 //     promotes into bf16); TMEM buffers are double-buffered so chunk k+1's MMAs overlap chunk k's
 //     promotion;
-//   * roles: 1 TMA thread (weights), 1 UMMA thread, 2 gather warps (token rows, cp.async with the
-//     128-byte swizzle applied by hand), 1-2 epilogue warpgroups.
+//   * roles: 2 gather warps (token rows by cp.async with the 128-byte swizzle applied by hand; lane 0
+//     of the first one also issues the weight TMA), 2 UMMA-issuing warps that take alternate chunks
+//     (one thread cannot issue eight UMMAs plus its barrier traffic fast enough to keep the tensor
+//     pipe busy), 1-2 epilogue warpgroups.
 //
 // Shared-memory ring slot: [256 weight rows x 128 B = 32 KB][token tile BMP x 128 B].
-//   up phase   : rows = the slice's 256 interleaved w rows of K-chunk `it`; token tile = x rows of the chunk
-//   down phase : rows = 256 consecutive hidden rows of w2 (the slice's 128 columns), i.e. two 128-row tiles
+//   up phase   : rows = one slice's 256 interleaved w rows of K-chunk kc; token tile = x rows of the chunk
+//   down phase : two 128-row x 128-byte tiles of w2 - SPC = 1: two consecutive hidden-row tiles of the
+//                slice; SPC = 2: the same 128 hidden rows for each of the two slices
 #pragma once
 
 #include "ptx_sm100.cuh"
@@ -43,7 +47,7 @@ struct MoeParams {
     float scaling;
     KernelStatus* status;
 #ifdef AMOE_TRACE
-    long long* trace;           // [12][KC+ND] clock64 stamps of one CTA (debug builds only)
+    long long* trace;           // [12][iterations] clock64 stamps of one CTA (debug builds only)
     int trace_block;
 #endif
 };
@@ -52,7 +56,7 @@ struct MoeParams {
 #define AMOE_STAMP(ev, it)                                                                   \
     do {                                                                                     \
         if (p.trace && static_cast<int>(blockIdx.x) == p.trace_block)                        \
-            p.trace[(ev) * (KC + ND) + (it)] = clock64();                                    \
+            p.trace[(ev) * NIT + (it)] = clock64();                                          \
     } while (0)
 #else
 #define AMOE_STAMP(ev, it) do { } while (0)
@@ -63,79 +67,83 @@ constexpr int kTileBytes = 128 * 128;  // one 128-row x 128-byte operand tile
 struct SmemPlan {
     uint32_t stage_bytes, hq, xs, swg, swu, sw2, tokrow, topkw, tokscale, amax, bars, misc, total;
 };
-// Offsets from a 1024-byte aligned base.  bmp = padded block_m, s = ring depth, kc = K/128.
-__host__ __device__ inline SmemPlan smem_plan(int bmp, int s, int kc) {
+// Offsets from a 1024-byte aligned base.  bmp = padded block_m, s = ring depth, kc = K/128,
+// spc = slices per CTA.
+__host__ __device__ inline SmemPlan smem_plan(int bmp, int s, int kc, int spc) {
     SmemPlan p;
     p.stage_bytes = 2 * kTileBytes + bmp * 128;
     uint32_t o = s * p.stage_bytes;
-    p.hq = o;        o += bmp * 128;
+    p.hq = o;        o += spc * bmp * 128;
     p.xs = o;        o += kc * bmp * 4;
-    p.swg = o;       o += kc * 4;
-    p.swu = o;       o += kc * 4;
-    p.sw2 = o;       o += kc * 4;
+    p.swg = o;       o += spc * kc * 4;
+    p.swu = o;       o += spc * kc * 4;
+    p.sw2 = o;       o += spc * kc * 4;
     o = (o + 15u) & ~15u;
     p.tokrow = o;    o += bmp * 4;
     p.topkw = o;     o += bmp * 4;
-    p.tokscale = o;  o += bmp * 4;
+    p.tokscale = o;  o += spc * bmp * 4;
     p.amax = o;      o += bmp * 16;
-    p.bars = o;      o += (2 * s + 5) * 8;
+    p.bars = o;      o += (2 * s + 7) * 8;
     p.misc = o;      o += 16;
     p.total = o;
     return p;
 }
 
-template <int LAGMAX>
 __device__ __forceinline__ void cp_async_wait_dyn(int n) {
     if (n <= 0) cp_async_wait<0>();
     else if (n == 1) cp_async_wait<1>();
     else cp_async_wait<2>();
 }
 
-template <int BMP>
-__global__ void __launch_bounds__(128 * (BMP >= 64 ? 2 : 1) + 128, 1)
+template <int BMP, int SPC>
+__global__ void __launch_bounds__(128 * (BMP >= 64 ? 2 : 1) + 128, BMP <= 32 ? 2 : 1)
 fused_moe_w8a8_up_down_sm100_kernel(const __grid_constant__ CUtensorMap tm_w,
                                     const __grid_constant__ CUtensorMap tm_w2, const MoeParams p) {
     constexpr int NEPI_WG = BMP >= 64 ? 2 : 1;   // epilogue warpgroups; each owns BMP/NEPI_WG token columns
     constexpr int NC = BMP / NEPI_WG;
     constexpr int EPI_THREADS = 128 * NEPI_WG;
-    constexpr int W_TMA = 4 * NEPI_WG, W_MMA = W_TMA + 1, W_G0 = W_TMA + 2;
-    constexpr uint32_t TMEM_COLS = 4 * BMP;      // two buffers x (gate|up) x BMP columns
+    constexpr int W_G0 = 4 * NEPI_WG, W_MMA0 = W_G0 + 2;   // control warpgroup: gather, gather, UMMA, UMMA
+    constexpr uint32_t TMEM_COLS = 4 * BMP;      // two buffers x two accumulators x BMP columns
     static_assert(BMP == 16 || BMP == 32 || BMP == 64 || BMP == 128, "padded block_m");
+    static_assert(SPC == 1 || SPC == 2, "slices per CTA");
 
-    const int nslices = p.N >> 8;
-    const int mblock = blockIdx.x / nslices;
-    const int slice = blockIdx.x - mblock * nslices;
+    const int ngroups = (p.N >> 8) / SPC;
+    const int mblock = blockIdx.x / ngroups;
+    const int slice0 = (blockIdx.x - mblock * ngroups) * SPC;
     const int npad = min(p.num_tokens_post_padded[0], p.sorted_num);
     if (mblock * p.block_m >= npad) return;          // block beyond the padded schedule (reference :678)
     const int expert = p.expert_ids[mblock];
     if (expert < 0 || expert >= p.E) return;
 
-    const int KC = p.K >> 7;           // 128-deep K chunks of the up-projection
-    const int ND = (KC + 1) >> 1;      // ring slots of the down-projection (two 128-row w2 tiles each)
+    const int KC = p.K >> 7;                         // 128-deep K chunks of the up-projection
+    const int UPI = SPC * KC;                        // up-projection iterations (slice-major)
+    const int ND = SPC == 1 ? (KC + 1) >> 1 : KC;    // down-projection iterations
+    const int NIT = UPI + ND;
     const int S = p.stages;
     const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
 
     extern __shared__ uint8_t smem_raw[];
     uint8_t* smem = smem_raw + ((1024u - (smem_u32(smem_raw) & 1023u)) & 1023u);
-    const SmemPlan L = smem_plan(BMP, S, KC);
-    uint8_t* hq = smem + L.hq;                                        // fp8 intermediate [BMP][128], swizzled
+    const SmemPlan L = smem_plan(BMP, S, KC, SPC);
+    uint8_t* hq = smem + L.hq;                                        // fp8 intermediate [SPC][BMP][128], swizzled
     float* xs = reinterpret_cast<float*>(smem + L.xs);                // [KC][BMP] token scales
-    float* swg = reinterpret_cast<float*>(smem + L.swg);              // [KC] gate block scales
-    float* swu = reinterpret_cast<float*>(smem + L.swu);              // [KC] up block scales
-    float* sw2 = reinterpret_cast<float*>(smem + L.sw2);              // [KC] w2 block scales (per 128 hidden rows)
+    float* swg = reinterpret_cast<float*>(smem + L.swg);              // [SPC][KC] gate block scales
+    float* swu = reinterpret_cast<float*>(smem + L.swu);              // [SPC][KC] up block scales
+    float* sw2 = reinterpret_cast<float*>(smem + L.sw2);              // [SPC][KC] w2 block scales per 128 hidden rows
     int* tokrow = reinterpret_cast<int*>(smem + L.tokrow);            // [BMP] row of x/out, or M if padding
     float* topkw = reinterpret_cast<float*>(smem + L.topkw);          // [BMP]
-    float* tokscale = reinterpret_cast<float*>(smem + L.tokscale);    // [BMP] s_h * topk_weight * scaling
+    float* tokscale = reinterpret_cast<float*>(smem + L.tokscale);    // [SPC][BMP] s_h * topk_weight * scaling
     uint32_t* amax_part = reinterpret_cast<uint32_t*>(smem + L.amax); // [BMP][4] per-warp |h| maxima
-    uint64_t* full = reinterpret_cast<uint64_t*>(smem + L.bars);   // slot filled: TMA bytes + 2 gather warps
-    uint64_t* empty = full + S;                                    // slot free again
+    uint64_t* full = reinterpret_cast<uint64_t*>(smem + L.bars);      // slot filled: TMA bytes + 2 gather warps
+    uint64_t* empty = full + S;                                       // slot free again
     uint64_t* acc_full = empty + S;
     uint64_t* acc_empty = acc_full + 2;
     uint64_t* h_ready = acc_empty + 2;
+    uint64_t* xchg = h_ready + 1;                                     // [2] amax exchange inside an epilogue warpgroup
     uint32_t* tmem_slot = reinterpret_cast<uint32_t*>(smem + L.misc);
     volatile int* abort_flag = reinterpret_cast<volatile int*>(smem + L.misc + 4);
 
-    if (threadIdx.x == W_TMA * 32) {
+    if (threadIdx.x == W_G0 * 32) {
         for (int i = 0; i < S; ++i) {
             mbar_init(&full[i], 3);
             mbar_init(&empty[i], 1);
@@ -145,10 +153,12 @@ fused_moe_w8a8_up_down_sm100_kernel(const __grid_constant__ CUtensorMap tm_w,
             mbar_init(&acc_empty[i], 4 * NEPI_WG);
         }
         mbar_init(h_ready, 1);
+        mbar_init(&xchg[0], 4);
+        mbar_init(&xchg[1], 4);
         *abort_flag = 0;
         fence_mbar_init();
     }
-    if (warp == W_MMA) {
+    if (warp == W_MMA0) {
         tmem_alloc(tmem_slot, TMEM_COLS);
         tmem_relinquish();
     }
@@ -157,83 +167,72 @@ fused_moe_w8a8_up_down_sm100_kernel(const __grid_constant__ CUtensorMap tm_w,
     tc_fence_after();
     const uint32_t tmem_base = *tmem_slot;
 
-    if (warp >= W_TMA) {
+    if (warp >= W_G0) {
     // ====================================================================== control warpgroup
     // The widest variant keeps 2 x 64 accumulators per epilogue thread: it moves registers from this
-    // warpgroup (TMA / UMMA / gather warps) to the two epilogue warpgroups.
+    // warpgroup to the two epilogue warpgroups.
     if constexpr (BMP == 128) setmaxnreg_dec<64>();
-    if (warp == W_TMA) {
-        // ------------------------------------------------------------------ weight producer
+    if (warp >= W_MMA0) {
+        // ------------------------------------------------------------------ UMMA issuers (even / odd chunks)
         if (lane == 0) {
-            prefetch_tmap(&tm_w);
-            prefetch_tmap(&tm_w2);
-            int s = 0;
-            uint32_t ph = 0;
-            uint8_t* st = smem;
-            for (int it = 0; it < KC + ND; ++it) {
-                AMOE_STAMP(7, it);
-                if (!mbar_wait(&empty[s], ph ^ 1, abort_flag, p.status, 10, it)) break;
-                AMOE_STAMP(0, it);
-                mbar_arrive_expect_tx(&full[s], 2 * kTileBytes);
-                if (it < KC) {  // 256 interleaved rows (128 gate + 128 up) x 128 bytes of K chunk `it`
-                    tma_load_3d(st, &tm_w, &full[s], it * 128, slice * 256, expert);
-                } else {        // 256 hidden rows x the slice's 128 columns of w2; rows past K arrive as zeros
-                    tma_load_3d(st, &tm_w2, &full[s], slice * 128, (it - KC) * 256, expert);
-                    mbar_arrive(&full[s]);   // no token gather in this phase: stand in for the two
-                    mbar_arrive(&full[s]);   // gather warps so that the barrier's count stays 3
-                }
-                AMOE_STAMP(6, it);
-                st += L.stage_bytes;
-                if (++s == S) { s = 0; ph ^= 1; st = smem; }
-            }
-        }
-    } else if (warp == W_MMA) {
-        // ------------------------------------------------------------------ UMMA issuer
-        if (lane == 0) {
+            const int pw = warp - W_MMA0;                                   // chunk parity = TMEM buffer
             constexpr uint32_t idesc = umma_idesc_e4m3(128, BMP);
-            const uint64_t hdesc = umma_desc_sw128(smem_u32(hq));
             const uint32_t st0 = smem_u32(smem);
             // Descriptors advance with the ring slot: only the 14-bit start-address field changes.
-            const uint64_t dstep = L.stage_bytes >> 4;
+            const uint32_t dstep = L.stage_bytes >> 4;
             const uint64_t a0_up0 = umma_desc_sw128(st0, 2048u);            // 8 gate rows of every 16
             const uint64_t a1_up0 = umma_desc_sw128(st0 + 1024u, 2048u);    // 8 up rows of every 16
             const uint64_t x_up0 = umma_desc_sw128(st0 + 2 * kTileBytes);   // gathered token rows
-            const uint64_t a0_dn0 = umma_desc_sw128(st0);                   // first 128 hidden rows of the slot
-            const uint64_t a1_dn0 = umma_desc_sw128(st0 + kTileBytes);      // second 128 hidden rows
-            int s = 0;
+            const uint64_t a0_dn0 = umma_desc_sw128(st0);                   // first w2 tile of the slot
+            const uint64_t a1_dn0 = umma_desc_sw128(st0 + kTileBytes);      // second w2 tile of the slot
+            const uint64_t h0 = umma_desc_sw128(smem_u32(hq));
+            const uint64_t h1 = umma_desc_sw128(smem_u32(hq + (SPC - 1) * BMP * 128));
+            // Two issuers take alternate chunks.  A parity wait can only tell "this phase" from "the one
+            // before", so the second issuer may start on chunk 1 only when chunk 1 is the first fill of
+            // its slot: with a one-slot ring the first issuer takes every chunk.
+            const int step = S > 1 ? 2 : 1;
+            int s = pw % S;
             uint32_t ph = 0;
-            uint64_t off = 0;
-            for (int it = 0; it < KC + ND; ++it) {
-                const int b = it & 1;
+            bool h_waited = false;
+            for (int it = pw; it < NIT && pw < step; it += step) {
+                const int b = it & 1;                                       // TMEM buffer of this chunk
                 const uint32_t aph = (it >> 1) & 1;
-                const bool up = it < KC;
+                const uint32_t d0 = tmem_base + b * 2 * BMP;
+                const bool up = it < UPI;
                 AMOE_STAMP(8, it);
-                if (it == KC && !mbar_wait(h_ready, 0, abort_flag, p.status, 20, it)) break;
+                if (!up && !h_waited) {
+                    if (!mbar_wait(h_ready, 0, abort_flag, p.status, 20, it)) break;
+                    h_waited = true;
+                }
                 if (!mbar_wait(&acc_empty[b], aph ^ 1, abort_flag, p.status, 21, it)) break;
                 AMOE_STAMP(9, it);
                 if (!mbar_wait(&full[s], ph, abort_flag, p.status, 22, it)) break;
                 tc_fence_after();
                 AMOE_STAMP(1, it);
-                const uint32_t d0 = tmem_base + b * 2 * BMP;
-                if (up)
-                    umma_f8_chunk2(d0, d0 + BMP, a0_up0 + off, a1_up0 + off, x_up0 + off, idesc);
-                else if (2 * (it - KC) + 1 < KC)
-                    umma_f8_chunk2(d0, d0 + BMP, a0_dn0 + off, a1_dn0 + off, hdesc, idesc);
-                else
-                    umma_f8_chunk1(d0, a0_dn0 + off, hdesc, idesc);
+                const uint64_t off = static_cast<uint64_t>(s * dstep);
+                if (up) {
+                    umma_f8_chunk2(d0, d0 + BMP, a0_up0 + off, a1_up0 + off, x_up0 + off, x_up0 + off, idesc);
+                } else if (SPC == 2) {
+                    umma_f8_chunk2(d0, d0 + BMP, a0_dn0 + off, a1_dn0 + off, h0, h1, idesc);
+                } else if (2 * (it - UPI) + 1 < KC) {
+                    umma_f8_chunk2(d0, d0 + BMP, a0_dn0 + off, a1_dn0 + off, h0, h0, idesc);
+                } else {
+                    umma_f8_chunk1(d0, a0_dn0 + off, h0, idesc);
+                }
                 AMOE_STAMP(11, it);
                 // One commit per chunk: the epilogue, once it sees the accumulators complete, also hands
                 // the ring slot back to the producers (the MMAs have finished reading it by then).
                 umma_commit(&acc_full[b]);
                 AMOE_STAMP(2, it);
-                off += dstep;
-                if (++s == S) { s = 0; ph ^= 1; off = 0; }
+                s += step;
+                while (s >= S) { s -= S; ph ^= 1; }
             }
         }
     } else {
-        // ------------------------------------------------------------------ token-row gather (2 warps)
+        // ------------------------------------------------------------------ token-row gather (2 warps) + weight TMA
         constexpr int PIECES = BMP / 8;             // 16-byte pieces per thread per chunk
         const int gtid = threadIdx.x - W_G0 * 32;   // 0..63
+        const bool tma_thread = gtid == 0;
         const int row0 = gtid >> 3, ch = gtid & 7;
         uint32_t src16[PIECES];                     // (row * K) / 16, or 0xFFFFFFFF for a padding row
 #pragma unroll
@@ -247,15 +246,28 @@ fused_moe_w8a8_up_down_sm100_kernel(const __grid_constant__ CUtensorMap tm_w,
                     src16[i] = static_cast<uint32_t>((static_cast<size_t>(pid / p.top_k) * p.K) >> 4);
             }
         }
+        if (tma_thread) {
+            prefetch_tmap(&tm_w);
+            prefetch_tmap(&tm_w2);
+        }
         const uint32_t dst0 = row0 * 128 + ((ch ^ (row0 & 7)) << 4);   // + i*1024 for piece i (row & 7 unchanged)
         const int lag = p.lag;
         bool ok = true;
-        int s = 0, sl = 0;                          // slot being filled / slot whose completion is signalled next
+        int s = 0, sl_sig = 0;                      // slot being filled / slot whose completion is signalled next
         uint32_t ph = 0;
-        for (int it = 0; it < KC; ++it) {
+        int kc = 0, sl = 0;
+        for (int it = 0; it < UPI; ++it) {
+            if (tma_thread) AMOE_STAMP(7, it);
             if (!mbar_wait(&empty[s], ph ^ 1, abort_flag, p.status, 30, it)) { ok = false; break; }
-            const uint32_t base = smem_u32(smem + s * L.stage_bytes + 2 * kTileBytes) + dst0;
-            const uint8_t* col = p.x + it * 128 + ch * 16;
+            uint8_t* st = smem + s * L.stage_bytes;
+            if (tma_thread) {
+                AMOE_STAMP(0, it);
+                mbar_arrive_expect_tx(&full[s], 2 * kTileBytes);
+                // 256 interleaved rows (128 gate + 128 up) of slice (slice0 + sl) x 128 bytes of K chunk kc
+                tma_load_3d(st, &tm_w, &full[s], kc * 128, (slice0 + sl) * 256, expert);
+            }
+            const uint32_t base = smem_u32(st + 2 * kTileBytes) + dst0;
+            const uint8_t* col = p.x + kc * 128 + ch * 16;
 #pragma unroll
             for (int i = 0; i < PIECES; ++i) {
                 const bool v = src16[i] != 0xFFFFFFFFu;
@@ -263,32 +275,54 @@ fused_moe_w8a8_up_down_sm100_kernel(const __grid_constant__ CUtensorMap tm_w,
                 cp_async_16(base + i * 1024, src, v ? 16u : 0u);
             }
             cp_async_commit();
-            if (gtid == 0) AMOE_STAMP(5, it);
             if (it >= lag) {
-                cp_async_wait_dyn<2>(lag);
+                cp_async_wait_dyn(lag);
                 fence_proxy_async_smem();
                 __syncwarp();
-                if (lane == 0) mbar_arrive(&full[sl]);
-                if (++sl == S) sl = 0;
+                if (lane == 0) mbar_arrive(&full[sl_sig]);
+                if (++sl_sig == S) sl_sig = 0;
             }
             if (++s == S) { s = 0; ph ^= 1; }
+            if (++kc == KC) { kc = 0; ++sl; }
         }
         cp_async_wait<0>();
         if (ok) {
             fence_proxy_async_smem();
             __syncwarp();
             if (lane == 0)
-                for (int it = max(KC - lag, 0); it < KC; ++it) {
-                    mbar_arrive(&full[sl]);
-                    if (++sl == S) sl = 0;
+                for (int it = max(UPI - lag, 0); it < UPI; ++it) {
+                    mbar_arrive(&full[sl_sig]);
+                    if (++sl_sig == S) sl_sig = 0;
                 }
+        }
+        if (tma_thread && ok) {
+            // down phase: this thread keeps feeding w2 tiles; there is no token gather any more, so it
+            // also stands in for the two gather warps on the slot's barrier (count 3)
+            for (int jt = 0; jt < ND; ++jt) {
+                const int it = UPI + jt;
+                AMOE_STAMP(7, it);
+                if (!mbar_wait(&empty[s], ph ^ 1, abort_flag, p.status, 10, it)) break;
+                uint8_t* st = smem + s * L.stage_bytes;
+                AMOE_STAMP(0, it);
+                mbar_arrive_expect_tx(&full[s], 2 * kTileBytes);
+                if (SPC == 1) {   // hidden rows [2jt*128, +256) of the slice's 128 columns; rows past K arrive as zeros
+                    tma_load_3d(st, &tm_w2, &full[s], slice0 * 128, (2 * jt) * 128, expert);
+                    tma_load_3d(st + kTileBytes, &tm_w2, &full[s], slice0 * 128, (2 * jt + 1) * 128, expert);
+                } else {          // hidden rows [jt*128, +128) for each of the two slices
+                    tma_load_3d(st, &tm_w2, &full[s], slice0 * 128, jt * 128, expert);
+                    tma_load_3d(st + kTileBytes, &tm_w2, &full[s], (slice0 + 1) * 128, jt * 128, expert);
+                }
+                mbar_arrive(&full[s]);
+                mbar_arrive(&full[s]);
+                if (++s == S) { s = 0; ph ^= 1; }
+            }
         }
     }
     } else {
         // ====================================================================== epilogue warpgroups
         if constexpr (BMP == 128) setmaxnreg_inc<216>();
         const int q = warp & 3;              // TMEM lane quarter this warp may read
-        const int hh = warp >> 2;            // which half of the token columns
+        const int hh = warp >> 2;            // which part of the token columns
         const int r = q * 32 + lane;         // weight row inside the tile = TMEM lane
         const int etid = threadIdx.x;
         const int mtk = p.M * p.top_k;
@@ -309,19 +343,19 @@ fused_moe_w8a8_up_down_sm100_kernel(const __grid_constant__ CUtensorMap tm_w,
         {
             const int nsr = p.N >> 7;                         // scale rows per expert in w_scale
             const int isl = p.N >> 8;                         // 128-column slices of the intermediate dim
-            const float* ws = p.w_scale + (static_cast<size_t>(expert) * nsr + 2 * slice) * KC;
-            const float* w2s = p.w2_scale + static_cast<size_t>(expert) * KC * isl + slice;
-            for (int i = etid; i < KC; i += EPI_THREADS) {
-                swg[i] = ws[i];                               // interleave slot 0 = gate (reference :919-925)
-                swu[i] = ws[KC + i];                          // slot 1 = up
-                sw2[i] = w2s[static_cast<size_t>(i) * isl];
+            for (int i = etid; i < SPC * KC; i += EPI_THREADS) {
+                const int sl = i / KC, c = i - sl * KC;
+                const float* ws = p.w_scale + (static_cast<size_t>(expert) * nsr + 2 * (slice0 + sl)) * KC;
+                swg[i] = ws[c];                               // interleave slot 0 = gate (reference :919-925)
+                swu[i] = ws[KC + c];                          // slot 1 = up
+                sw2[i] = p.w2_scale[(static_cast<size_t>(expert) * KC + c) * isl + slice0 + sl];
             }
         }
         named_bar_sync(1, EPI_THREADS);
         for (int i = etid; i < BMP * KC; i += EPI_THREADS) {
-            const int j = i / KC, kc = i - j * KC;
+            const int j = i / KC, c = i - j * KC;
             const int row = tokrow[j];
-            xs[kc * BMP + j] = row < p.M ? p.x_scale[static_cast<size_t>(row) * KC + kc] : 0.f;
+            xs[c * BMP + j] = row < p.M ? p.x_scale[static_cast<size_t>(row) * KC + c] : 0.f;
         }
         int nhi = 0;
         for (int j = 0; j < BMP; ++j)
@@ -333,11 +367,20 @@ fused_moe_w8a8_up_down_sm100_kernel(const __grid_constant__ CUtensorMap tm_w,
 #pragma unroll
         for (int j = 0; j < NC; ++j) accg[j] = accu[j] = 0.f;
 
+        // Factor of column j for the output = s_h * topk weight * scaling (reference :997-1003) and its row
+        // in `out` (M = padding): in registers for the narrow single-slice variants, else in shared memory.
+        constexpr bool kFactorsInRegs = (NC <= 16) && (SPC == 1);
+        constexpr int NF = kFactorsInRegs ? NC : 2;
+        int rowj[NF];
+        float facj[NF];
+
         const uint32_t tlane = tmem_base + (static_cast<uint32_t>(q * 32) << 16) + hh * NC;
         bool ok = true;
         int es = 0;                          // ring slot of the chunk being retired (for handing it back)
+        int kc = 0, sl = 0;
+        uint32_t xph = 0;
         // ---- up-projection: promote each K chunk with its scales (reference :915-933)
-        for (int it = 0; it < KC; ++it) {
+        for (int it = 0; it < UPI && ok; ++it) {
             const int b = it & 1;
             const uint32_t aph = (it >> 1) & 1;
             if (!mbar_wait(&acc_full[b], aph, abort_flag, p.status, 40, it)) { ok = false; break; }
@@ -345,7 +388,7 @@ fused_moe_w8a8_up_down_sm100_kernel(const __grid_constant__ CUtensorMap tm_w,
             if (++es == S) es = 0;
             tc_fence_after();
             if (etid == 0) AMOE_STAMP(3, it);
-            const float sg = swg[it], su = swu[it];
+            const float sg = swg[sl * KC + kc], su = swu[sl * KC + kc];
             const uint32_t tb = tlane + b * 2 * BMP;
 #pragma unroll
             for (int c0 = 0; c0 < NC; c0 += 16) {
@@ -354,7 +397,7 @@ fused_moe_w8a8_up_down_sm100_kernel(const __grid_constant__ CUtensorMap tm_w,
                     tmem_ld16(tb + c0, vg);
                     tmem_ld16(tb + BMP + c0, vu);
                     tmem_ld_wait();
-                    const float4* sx4 = reinterpret_cast<const float4*>(xs + it * BMP + hh * NC + c0);
+                    const float4* sx4 = reinterpret_cast<const float4*>(xs + kc * BMP + hh * NC + c0);
 #pragma unroll
                     for (int jj = 0; jj < 4; ++jj) {
                         const float4 sx = sx4[jj];
@@ -372,66 +415,71 @@ fused_moe_w8a8_up_down_sm100_kernel(const __grid_constant__ CUtensorMap tm_w,
             __syncwarp();
             if (lane == 0) mbar_arrive(&acc_empty[b]);
             if (etid == 0) AMOE_STAMP(4, it);
-        }
 
-        // ---- SwiGLU, per-token amax over the 128 columns of the slice, fp8 re-quantisation
-        //      (reference :936-1005; here h stays in registers, only the fp8 tile goes to shared memory)
+            if (++kc == KC) {
+                // ---- end of a slice: SwiGLU, per-token amax over the slice's 128 columns, fp8 re-quantisation
+                //      (reference :936-1005; h stays in registers, only the fp8 tile goes to shared memory)
 #pragma unroll
-        for (int j = 0; j < NC; ++j) {
-            const float g = bf16_round(accg[j]);
-            const float u = bf16_round(accu[j]);
-            const float h = bf16_round(__fdividef(g, 1.0f + __expf(-g)) * u);
-            accg[j] = h;
-            const uint32_t a = __reduce_max_sync(0xFFFFFFFFu, __float_as_uint(fabsf(h)));
-            if (lane == 0) amax_part[(hh * NC + j) * 4 + q] = a;
-        }
-        named_bar_sync(2 + hh, 128);
-        // Factor of column j for the output = s_h * topk weight * scaling (reference :997-1003), and its
-        // row in `out` (M = padding): kept in registers, except in the widest variant where the registers
-        // are needed for the accumulators and the pair comes from shared memory instead.
-        constexpr bool kFactorsInRegs = NC <= 32;
-        constexpr int NF = kFactorsInRegs ? NC : 2;
-        int rowj[NF];
-        float facj[NF];
+                for (int j = 0; j < NC; ++j) {
+                    const float g = bf16_round(accg[j]);
+                    const float u = bf16_round(accu[j]);
+                    const float h = bf16_round(__fdividef(g, 1.0f + __expf(-g)) * u);
+                    accg[j] = h;
+                    const uint32_t a = __reduce_max_sync(0xFFFFFFFFu, __float_as_uint(fabsf(h)));
+                    if (lane == 0) amax_part[(hh * NC + j) * 4 + q] = a;
+                }
+                // exchange of the four warps' maxima through a (bounded) mbarrier rather than bar.sync, so that
+                // a warp that gave up on a wait can never leave the others parked at a hardware barrier
+                __syncwarp();
+                if (lane == 0) mbar_arrive(&xchg[hh]);
+                if (!mbar_wait(&xchg[hh], xph, abort_flag, p.status, 42, it)) ok = false;
+                xph ^= 1;
+                uint8_t* hq_sl = hq + sl * BMP * 128;
 #pragma unroll
-        for (int j = 0; j < NC; ++j) {
-            const int col = hh * NC + j;
-            const uint4 pm = *reinterpret_cast<const uint4*>(amax_part + col * 4);
-            const float amax = __uint_as_float(max(max(pm.x, pm.y), max(pm.z, pm.w)));
-            const float s_h = fmaxf(amax, 1e-10f) * (1.0f / 448.0f);
-            const float qv = fminf(fmaxf(__fdividef(accg[j], s_h), -448.0f), 448.0f);
-            const uint8_t qb = static_cast<uint8_t>(__nv_cvt_float_to_fp8(qv, __NV_SATFINITE, __NV_E4M3));
-            hq[col * 128 + ((((r >> 4) ^ (col & 7)) << 4) | (r & 15))] = qb;
-            const float fac = s_h * topkw[col] * p.scaling;
-            if constexpr (kFactorsInRegs) {
-                facj[j] = fac;
-                rowj[j] = tokrow[col];
-            } else {
-                if (r == 0) tokscale[col] = fac;
+                for (int j = 0; j < NC; ++j) {
+                    const int col = hh * NC + j;
+                    const uint4 pm = *reinterpret_cast<const uint4*>(amax_part + col * 4);
+                    const float amax = __uint_as_float(max(max(pm.x, pm.y), max(pm.z, pm.w)));
+                    const float s_h = fmaxf(amax, 1e-10f) * (1.0f / 448.0f);
+                    const float qv = fminf(fmaxf(__fdividef(accg[j], s_h), -448.0f), 448.0f);
+                    const uint8_t qb = static_cast<uint8_t>(__nv_cvt_float_to_fp8(qv, __NV_SATFINITE, __NV_E4M3));
+                    hq_sl[col * 128 + ((((r >> 4) ^ (col & 7)) << 4) | (r & 15))] = qb;
+                    const float fac = s_h * topkw[col] * p.scaling;
+                    if constexpr (kFactorsInRegs) {
+                        facj[j] = fac;
+                        rowj[j] = tokrow[col];
+                    } else {
+                        if (r == 0) tokscale[sl * BMP + col] = fac;
+                    }
+                    accg[j] = 0.f;
+                    accu[j] = 0.f;
+                }
+                fence_proxy_async_smem();
+                // (amax_part is rewritten at the end of the next slice; the acc_empty hand-shake keeps the four
+                //  warps within two chunks of each other, so every read above has long completed by then)
+                kc = 0;
+                ++sl;
             }
         }
-        fence_proxy_async_smem();
         named_bar_sync(1, EPI_THREADS);
         if (etid == 0) mbar_arrive(h_ready);
 
         // ---- down-projection epilogue: scale, pair adjacent hidden columns, bf16x2 reduce into out
         //      (reference :1052-1094 goes through stmatrix + per-row bulk reduce).
-        // The accumulators are copied to registers and handed back to the MMA thread *before* any
+        // The accumulators are copied to registers and handed back to the MMA warps *before* any
         // reduction is issued: tcgen05.fence / mbarrier.arrive after a global reduction would wait for
         // L2 to acknowledge it, which would put an L2 round trip into every iteration.
         const bool odd = lane & 1;
         for (int jt = 0; jt < ND && ok; ++jt) {
-            const int it = KC + jt;
+            const int it = UPI + jt;
             const int b = it & 1;
             const uint32_t aph = (it >> 1) & 1;
-            if (etid == 0) AMOE_STAMP(6, it);
             if (!mbar_wait(&acc_full[b], aph, abort_flag, p.status, 41, it)) { ok = false; break; }
-            if (etid == 0) AMOE_STAMP(10, it);
             if (etid == 0) mbar_arrive_relaxed(&empty[es]);
             if (++es == S) es = 0;
             tc_fence_after();
             if (etid == 0) AMOE_STAMP(3, it);
-            const bool two = 2 * jt + 1 < KC;
+            const bool two = SPC == 2 || (2 * jt + 1 < KC);
             const uint32_t tb = tlane + b * 2 * BMP;
             uint32_t v0[NC], v1[NC];
 #pragma unroll
@@ -446,36 +494,65 @@ fused_moe_w8a8_up_down_sm100_kernel(const __grid_constant__ CUtensorMap tm_w,
             __syncwarp();
             if (lane == 0) mbar_arrive_relaxed(&acc_empty[b]);
             if (etid == 0) AMOE_STAMP(4, it);
+
+            if constexpr (SPC == 1) {
+                // v0 / v1 = hidden tiles 2jt and 2jt+1 of the same slice
 #pragma unroll
-            for (int tt = 0; tt < 2; ++tt) {
-                if (tt == 0 || two) {
-                    const int tile = 2 * jt + tt;
-                    const float s2 = sw2[tile];
-                    __nv_bfloat16* obase = p.out + tile * 128 + (r & ~1);
-                    // Straight-line over each live 16-column group (padding columns carry row == M and
-                    // are masked at the reduction): per-pair branches would serialise this single warp.
+                for (int tt = 0; tt < 2; ++tt) {
+                    if (tt == 0 || two) {
+                        const int tile = 2 * jt + tt;
+                        const float s2 = sw2[tile];
+                        __nv_bfloat16* obase = p.out + tile * 128 + (r & ~1);
+                        // Straight-line over each live 16-column group (padding columns carry row == M and are
+                        // masked at the reduction): per-pair branches would serialise this single warp.
 #pragma unroll
-                    for (int c0 = 0; c0 < NC; c0 += 16) {
-                        if (c0 < my_ncols) {
+                        for (int c0 = 0; c0 < NC; c0 += 16) {
+                            if (c0 < my_ncols) {
 #pragma unroll
-                            for (int j = c0; j < c0 + 16; j += 2) {
-                                float f0, f1;
-                                int r0, r1;
-                                if constexpr (kFactorsInRegs) {
-                                    f0 = facj[j]; f1 = facj[j + 1]; r0 = rowj[j]; r1 = rowj[j + 1];
-                                } else {
-                                    const float2 ff = *reinterpret_cast<const float2*>(tokscale + hh * NC + j);
-                                    const int2 rr = *reinterpret_cast<const int2*>(tokrow + hh * NC + j);
-                                    f0 = ff.x; f1 = ff.y; r0 = rr.x; r1 = rr.y;
+                                for (int j = c0; j < c0 + 16; j += 2) {
+                                    float f0, f1;
+                                    int r0, r1;
+                                    if constexpr (kFactorsInRegs) {
+                                        f0 = facj[j]; f1 = facj[j + 1]; r0 = rowj[j]; r1 = rowj[j + 1];
+                                    } else {
+                                        const float2 ff = *reinterpret_cast<const float2*>(tokscale + hh * NC + j);
+                                        const int2 rr = *reinterpret_cast<const int2*>(tokrow + hh * NC + j);
+                                        f0 = ff.x; f1 = ff.y; r0 = rr.x; r1 = rr.y;
+                                    }
+                                    const float a = __uint_as_float(tt ? v1[j] : v0[j]) * (s2 * f0);
+                                    const float bb = __uint_as_float(tt ? v1[j + 1] : v0[j + 1]) * (s2 * f1);
+                                    const float recv = __shfl_xor_sync(0xFFFFFFFFu, odd ? a : bb, 1);
+                                    const float lo = odd ? recv : a;
+                                    const float hi = odd ? bb : recv;
+                                    const int row = odd ? r1 : r0;
+                                    red_add_bf16x2_if(obase + static_cast<size_t>(row) * p.K, lo, hi, row, p.M);
                                 }
-                                const float a = __uint_as_float(tt ? v1[j] : v0[j]) * (s2 * f0);
-                                const float bb = __uint_as_float(tt ? v1[j + 1] : v0[j + 1]) * (s2 * f1);
-                                const float recv = __shfl_xor_sync(0xFFFFFFFFu, odd ? a : bb, 1);
-                                const float lo = odd ? recv : a;
-                                const float hi = odd ? bb : recv;
-                                const int row = odd ? r1 : r0;
-                                red_add_bf16x2_if(obase + static_cast<size_t>(row) * p.K, lo, hi, row, p.M);
                             }
+                        }
+                    }
+                }
+            } else {
+                // v0 / v1 = partial sums of hidden tile jt over slice 0 / slice 1: each has its own block scale
+                // and its own per-token quantisation scale, so they are combined here, then reduced once
+                const float s2a = sw2[jt], s2b = sw2[KC + jt];
+                __nv_bfloat16* obase = p.out + jt * 128 + (r & ~1);
+#pragma unroll
+                for (int c0 = 0; c0 < NC; c0 += 16) {
+                    if (c0 < my_ncols) {
+#pragma unroll
+                        for (int j = c0; j < c0 + 16; j += 2) {
+                            const float2 fa = *reinterpret_cast<const float2*>(tokscale + hh * NC + j);
+                            const float2 fb = *reinterpret_cast<const float2*>(tokscale + BMP + hh * NC + j);
+                            const int2 rr = *reinterpret_cast<const int2*>(tokrow + hh * NC + j);
+                            const float a = fmaf(__uint_as_float(v0[j]), s2a * fa.x,
+                                                 __uint_as_float(v1[j]) * (s2b * fb.x));
+                            const float bb = fmaf(__uint_as_float(v0[j + 1]), s2a * fa.y,
+                                                  __uint_as_float(v1[j + 1]) * (s2b * fb.y));
+                            const float recv = __shfl_xor_sync(0xFFFFFFFFu, odd ? a : bb, 1);
+                            const float lo = odd ? recv : a;
+                            const float hi = odd ? bb : recv;
+                            const int row = odd ? rr.y : rr.x;
+                            red_add_bf16x2_if(obase + static_cast<size_t>(row) * p.K, lo, hi, row, p.M);
                         }
                     }
                 }
@@ -486,7 +563,7 @@ fused_moe_w8a8_up_down_sm100_kernel(const __grid_constant__ CUtensorMap tm_w,
 
     tc_fence_before();
     __syncthreads();
-    if (warp == W_MMA) {
+    if (warp == W_MMA0) {
         tc_fence_after();
         tmem_dealloc(tmem_base, TMEM_COLS);
     }

@@ -99,10 +99,10 @@ int get_maps(int device, const void* w, const void* w2, int E, int N, int K, con
         if (r != CUDA_SUCCESS) return fail(ALPHA_MOE_E_CUDA, "cuTensorMapEncodeTiled(w) failed with CUresult %d", (int)r);
     }
     {
-        // w2 [E][K][I]: box = 256 hidden rows x 128 bytes of one intermediate slice; rows past K read zero.
+        // w2 [E][K][I]: box = 128 hidden rows x 128 bytes of one intermediate slice; rows past K read zero.
         cuuint64_t dims[3] = {I, Kk, static_cast<cuuint64_t>(E)};
         cuuint64_t strides[2] = {I, Kk * I};
-        cuuint32_t box[3] = {128, 256, 1};
+        cuuint32_t box[3] = {128, 128, 1};
         cuuint32_t estr[3] = {1, 1, 1};
         CUresult r = enc(&mp.w2, CU_TENSOR_MAP_DATA_TYPE_UINT8, 3, const_cast<void*>(w2), dims, strides, box, estr,
                          CU_TENSOR_MAP_INTERLEAVE_NONE, CU_TENSOR_MAP_SWIZZLE_128B, CU_TENSOR_MAP_L2_PROMOTION_L2_256B,
@@ -120,12 +120,12 @@ constexpr int kMaxDynSmem = 232448;  // 227 KB opt-in limit per CTA on sm_100
 int padded_block_m(int block_m) { return block_m <= 16 ? 16 : block_m <= 32 ? 32 : block_m <= 64 ? 64 : 128; }
 
 // Ring depth = the `stages` knob, lowered until the plan fits in shared memory.
-int plan(int K, int block_m, int stages, int* depth, int* bmp, int* smem_bytes) {
+int plan(int K, int block_m, int stages, int spc, int* depth, int* bmp, int* smem_bytes) {
     const int kc = K / 128;
     const int b = padded_block_m(block_m);
     int s = stages;
     for (; s >= 1; --s) {
-        const int need = static_cast<int>(amoe::smem_plan(b, s, kc).total) + 1024;
+        const int need = static_cast<int>(amoe::smem_plan(b, s, kc, spc).total) + 1024;
         if (need <= kMaxDynSmem) {
             *depth = s;
             *bmp = b;
@@ -136,10 +136,10 @@ int plan(int K, int block_m, int stages, int* depth, int* bmp, int* smem_bytes) 
     return fail(ALPHA_MOE_E_ARG, "K=%d block_m=%d does not fit in shared memory even with one stage", K, block_m);
 }
 
-template <int BMP>
+template <int BMP, int SPC>
 int launch_variant(const CUtensorMap& mw, const CUtensorMap& mw2, const amoe::MoeParams& p, int grid, int smem_bytes,
                    cudaStream_t stream) {
-    auto kern = amoe::fused_moe_w8a8_up_down_sm100_kernel<BMP>;
+    auto kern = amoe::fused_moe_w8a8_up_down_sm100_kernel<BMP, SPC>;
     static int configured_smem[64] = {0};   // per device: largest dynamic smem size already opted in
     int dev = 0;
     CUDA_TRY(cudaGetDevice(&dev));
@@ -181,8 +181,11 @@ int alpha_moe_b200_fused_moe_w8a8_up_down(const void* x, const float* x_scale, c
     if (reinterpret_cast<uintptr_t>(out) & 3) return fail(ALPHA_MOE_E_ARG, "out must be 4-byte aligned");
     if (static_cast<long long>(M) * top_k > 0x7FFFFFFFLL) return fail(ALPHA_MOE_E_ARG, "M*top_k overflows int32");
 
+    // block_n = 64 asks for the wide variant: one CTA owns two 128-column slices of the intermediate
+    // dimension (one reduction per token and expert instead of two); it needs an even slice count.
+    const int spc = (block_n == 64 && (N / 256) % 2 == 0) ? 2 : 1;
     int depth, bmp, smem_bytes;
-    if (int rc = plan(K, block_m, stages, &depth, &bmp, &smem_bytes)) return rc;
+    if (int rc = plan(K, block_m, stages, spc, &depth, &bmp, &smem_bytes)) return rc;
 
     int dev = 0;
     CUDA_TRY(cudaGetDevice(&dev));
@@ -219,14 +222,23 @@ int alpha_moe_b200_fused_moe_w8a8_up_down(const void* x, const float* x_scale, c
 #endif
 
     const long long nblocks = (static_cast<long long>(sorted_num) + block_m - 1) / block_m;
-    const long long grid = nblocks * (N / 256);
+    const long long grid = nblocks * (N / 256 / spc);
     if (grid > 0x7FFFFFFFLL) return fail(ALPHA_MOE_E_ARG, "grid too large");
     cudaStream_t st = static_cast<cudaStream_t>(stream);
+    const int g = static_cast<int>(grid);
+    if (spc == 1) {
+        switch (bmp) {
+            case 16: return launch_variant<16, 1>(maps->w, maps->w2, p, g, smem_bytes, st);
+            case 32: return launch_variant<32, 1>(maps->w, maps->w2, p, g, smem_bytes, st);
+            case 64: return launch_variant<64, 1>(maps->w, maps->w2, p, g, smem_bytes, st);
+            default: return launch_variant<128, 1>(maps->w, maps->w2, p, g, smem_bytes, st);
+        }
+    }
     switch (bmp) {
-        case 16: return launch_variant<16>(maps->w, maps->w2, p, static_cast<int>(grid), smem_bytes, st);
-        case 32: return launch_variant<32>(maps->w, maps->w2, p, static_cast<int>(grid), smem_bytes, st);
-        case 64: return launch_variant<64>(maps->w, maps->w2, p, static_cast<int>(grid), smem_bytes, st);
-        default: return launch_variant<128>(maps->w, maps->w2, p, static_cast<int>(grid), smem_bytes, st);
+        case 16: return launch_variant<16, 2>(maps->w, maps->w2, p, g, smem_bytes, st);
+        case 32: return launch_variant<32, 2>(maps->w, maps->w2, p, g, smem_bytes, st);
+        case 64: return launch_variant<64, 2>(maps->w, maps->w2, p, g, smem_bytes, st);
+        default: return launch_variant<128, 2>(maps->w, maps->w2, p, g, smem_bytes, st);
     }
 }
 
@@ -246,16 +258,19 @@ int alpha_moe_b200_read_status(int32_t* out4, int reset) {
     return ALPHA_MOE_OK;
 }
 
-int alpha_moe_b200_plan(int K, int block_m, int stages, int32_t* out3) {
-    if (!out3) return fail(ALPHA_MOE_E_ARG, "out3 is null");
+int alpha_moe_b200_plan(int K, int block_m, int block_n, int stages, int32_t* out4) {
+    if (!out4) return fail(ALPHA_MOE_E_ARG, "out4 is null");
     if (K <= 0 || K % 128 != 0) return fail(ALPHA_MOE_E_ARG, "K dimension must be a multiple of 128 (K=%d)", K);
     if (block_m < 8 || block_m > 128 || block_m % 8 != 0) return fail(ALPHA_MOE_E_ARG, "bad block_m %d", block_m);
+    if (block_n != 32 && block_n != 64) return fail(ALPHA_MOE_E_ARG, "block_n must be 32 or 64, got %d", block_n);
     if (stages < 1 || stages > 5) return fail(ALPHA_MOE_E_ARG, "stages must be in 1..5, got %d", stages);
+    const int spc = block_n == 64 ? 2 : 1;
     int depth, bmp, smem_bytes;
-    if (int rc = plan(K, block_m, stages, &depth, &bmp, &smem_bytes)) return rc;
-    out3[0] = depth;
-    out3[1] = bmp;
-    out3[2] = smem_bytes;
+    if (int rc = plan(K, block_m, stages, spc, &depth, &bmp, &smem_bytes)) return rc;
+    out4[0] = depth;
+    out4[1] = bmp;
+    out4[2] = smem_bytes;
+    out4[3] = spc;
     return ALPHA_MOE_OK;
 }
 

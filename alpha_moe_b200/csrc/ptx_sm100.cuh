@@ -150,27 +150,27 @@ __device__ __forceinline__ uint64_t umma_desc_sw128(uint32_t smem_addr, uint32_t
 __host__ __device__ constexpr uint32_t umma_idesc_e4m3(uint32_t m, uint32_t n) {
     return (1u << 4) | ((n >> 3) << 17) | ((m >> 4) << 24);
 }
-// One 128-deep K chunk (four K=32 steps) of two independent accumulators that share the B operand:
-//   D0 = A0 * B, D1 = A1 * B   (fresh accumulation: the first step overwrites D).
+// One 128-deep K chunk (four K=32 steps) of two independent accumulators:
+//   D0 = A0 * B0, D1 = A1 * B1   (fresh accumulation: the first step overwrites D).
 // All eight instructions sit in one asm block so that the issuing thread spends no instructions
 // between them; descriptors advance by 32 bytes (2 in units of 16 B) per K step.
-__device__ __forceinline__ void umma_f8_chunk2(uint32_t d0, uint32_t d1, uint64_t a0, uint64_t a1, uint64_t b,
-                                               uint32_t idesc) {
+__device__ __forceinline__ void umma_f8_chunk2(uint32_t d0, uint32_t d1, uint64_t a0, uint64_t a1, uint64_t b0,
+                                               uint64_t b1, uint32_t idesc) {
     asm volatile(
-        "{\n\t.reg .pred pf, pt;\n\t.reg .b64 a0k, a1k, bk;\n\t"
+        "{\n\t.reg .pred pf, pt;\n\t.reg .b64 a0k, a1k, b0k, b1k;\n\t"
         "setp.ne.b32 pf, 0, 0;\n\tsetp.eq.b32 pt, 0, 0;\n\t"
-        "tcgen05.mma.cta_group::1.kind::f8f6f4 [%0], %2, %4, %5, pf;\n\t"
-        "tcgen05.mma.cta_group::1.kind::f8f6f4 [%1], %3, %4, %5, pf;\n\t"
-        "add.u64 a0k, %2, 2;\n\tadd.u64 a1k, %3, 2;\n\tadd.u64 bk, %4, 2;\n\t"
-        "tcgen05.mma.cta_group::1.kind::f8f6f4 [%0], a0k, bk, %5, pt;\n\t"
-        "tcgen05.mma.cta_group::1.kind::f8f6f4 [%1], a1k, bk, %5, pt;\n\t"
-        "add.u64 a0k, %2, 4;\n\tadd.u64 a1k, %3, 4;\n\tadd.u64 bk, %4, 4;\n\t"
-        "tcgen05.mma.cta_group::1.kind::f8f6f4 [%0], a0k, bk, %5, pt;\n\t"
-        "tcgen05.mma.cta_group::1.kind::f8f6f4 [%1], a1k, bk, %5, pt;\n\t"
-        "add.u64 a0k, %2, 6;\n\tadd.u64 a1k, %3, 6;\n\tadd.u64 bk, %4, 6;\n\t"
-        "tcgen05.mma.cta_group::1.kind::f8f6f4 [%0], a0k, bk, %5, pt;\n\t"
-        "tcgen05.mma.cta_group::1.kind::f8f6f4 [%1], a1k, bk, %5, pt;\n\t}"
-        ::"r"(d0), "r"(d1), "l"(a0), "l"(a1), "l"(b), "r"(idesc)
+        "tcgen05.mma.cta_group::1.kind::f8f6f4 [%0], %2, %4, %6, pf;\n\t"
+        "tcgen05.mma.cta_group::1.kind::f8f6f4 [%1], %3, %5, %6, pf;\n\t"
+        "add.u64 a0k, %2, 2;\n\tadd.u64 a1k, %3, 2;\n\tadd.u64 b0k, %4, 2;\n\tadd.u64 b1k, %5, 2;\n\t"
+        "tcgen05.mma.cta_group::1.kind::f8f6f4 [%0], a0k, b0k, %6, pt;\n\t"
+        "tcgen05.mma.cta_group::1.kind::f8f6f4 [%1], a1k, b1k, %6, pt;\n\t"
+        "add.u64 a0k, %2, 4;\n\tadd.u64 a1k, %3, 4;\n\tadd.u64 b0k, %4, 4;\n\tadd.u64 b1k, %5, 4;\n\t"
+        "tcgen05.mma.cta_group::1.kind::f8f6f4 [%0], a0k, b0k, %6, pt;\n\t"
+        "tcgen05.mma.cta_group::1.kind::f8f6f4 [%1], a1k, b1k, %6, pt;\n\t"
+        "add.u64 a0k, %2, 6;\n\tadd.u64 a1k, %3, 6;\n\tadd.u64 b0k, %4, 6;\n\tadd.u64 b1k, %5, 6;\n\t"
+        "tcgen05.mma.cta_group::1.kind::f8f6f4 [%0], a0k, b0k, %6, pt;\n\t"
+        "tcgen05.mma.cta_group::1.kind::f8f6f4 [%1], a1k, b1k, %6, pt;\n\t}"
+        ::"r"(d0), "r"(d1), "l"(a0), "l"(a1), "l"(b0), "l"(b1), "r"(idesc)
         : "memory");
 }
 // Same for a single accumulator.

@@ -43,9 +43,11 @@ def best_knobs(m: int):
     if os.path.exists(path):
         c = get_best_config(path, m)
         return c["block_m"], c["block_n"], c["warp_n"], c["stages"]
+    if m <= 8:
+        return 16, 32, 8, 5
     if m <= 256:
         return 16, 32, 8, 3
-    return 64, 32, 8, 5
+    return 64, 64, 4, 5
 
 
 def load_peaks():

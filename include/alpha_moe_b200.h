@@ -33,6 +33,8 @@ extern "C" {
  * block_m is semantic (the block size given to moe_align_block_size); block_n/warp_n/stages are the
  * reference's tuning knobs and are validated like csrc/torch_interface.cpp:62-64:
  * (block_n,warp_n) in {(64,4),(32,8)}, 1 <= stages <= 5, block_m in {8,16,...,128}.
+ * Here stages = depth of the shared-memory ring (lowered if it would not fit), and block_n = 64
+ * selects the variant in which one CTA owns two 128-column slices of the intermediate dimension.
  * Requires K % 128 == 0, N % 256 == 0, 16-byte aligned w / w2 / x. */
 int alpha_moe_b200_fused_moe_w8a8_up_down(
     const void* x, const float* x_scale, const void* w, const float* w_scale, const void* w2,
@@ -45,9 +47,10 @@ int alpha_moe_b200_fused_moe_w8a8_up_down(
  * code 0 means no kernel wait has ever run out.  Synchronises the device. */
 int alpha_moe_b200_read_status(int32_t* out4, int reset);
 
-/* Ring depth, padded block_m and dynamic shared memory the launcher would use; for tuners and tests.
- * out3 = {ring_depth, padded_block_m, dynamic_smem_bytes}.  No device work. */
-int alpha_moe_b200_plan(int K, int block_m, int stages, int32_t* out3);
+/* What the launcher would use for these knobs; for tuners and tests.  out4 = {ring_depth,
+ * padded_block_m, dynamic_smem_bytes, slices_per_cta (2 when block_n = 64 and N/256 is even)}.
+ * No device work. */
+int alpha_moe_b200_plan(int K, int block_m, int block_n, int stages, int32_t* out4);
 
 const char* alpha_moe_b200_last_error(void);
 const char* alpha_moe_b200_version(void);

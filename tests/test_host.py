@@ -94,9 +94,10 @@ def test_plan_fits_shared_memory_for_every_knob():
     for k in (128, 2048, 4096, 7168):
         for bm in range(8, 129, 8):
             for st in range(1, 6):
-                depth, bmp, smem = capi.plan(k, bm, st)
-                assert 1 <= depth <= st and bmp >= bm and bmp in (16, 32, 64, 128)
-                assert smem <= 232448
+                for bn in (32, 64):
+                    depth, bmp, smem, spc = capi.plan(k, bm, st, bn)
+                    assert 1 <= depth <= st and bmp >= bm and bmp in (16, 32, 64, 128)
+                    assert smem <= 232448 and spc == (2 if bn == 64 else 1)
     assert capi.plan(7168, 16, 5)[0] == 5
 
 
