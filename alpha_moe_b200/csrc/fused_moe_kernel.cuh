@@ -43,7 +43,6 @@ struct MoeParams {
     const float* topk_weights;  // [M, top_k]
     int top_k, M, K, N, E, sorted_num, block_m;
     int stages;                 // ring depth actually used (fits in shared memory)
-    int lag;                    // gather completion is signalled `lag` chunks late (< stages)
     float scaling;
     KernelStatus* status;
 #ifdef AMOE_TRACE
@@ -89,12 +88,6 @@ __host__ __device__ inline SmemPlan smem_plan(int bmp, int s, int kc, int spc) {
     return p;
 }
 
-__device__ __forceinline__ void cp_async_wait_dyn(int n) {
-    if (n <= 0) cp_async_wait<0>();
-    else if (n == 1) cp_async_wait<1>();
-    else cp_async_wait<2>();
-}
-
 template <int BMP, int SPC>
 __global__ void __launch_bounds__(128 * (BMP >= 64 ? 2 : 1) + 128, BMP <= 32 ? 2 : 1)
 fused_moe_w8a8_up_down_sm100_kernel(const __grid_constant__ CUtensorMap tm_w,
@@ -122,8 +115,15 @@ fused_moe_w8a8_up_down_sm100_kernel(const __grid_constant__ CUtensorMap tm_w,
     const int S = p.stages;
     const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
 
-    extern __shared__ uint8_t smem_raw[];
-    uint8_t* smem = smem_raw + ((1024u - (smem_u32(smem_raw) & 1023u)) & 1023u);
+    // The operand tiles need 1024-byte alignment (128-byte swizzle atoms).  The dynamic shared memory
+    // window is declared with that alignment; should a toolchain ever place it differently, the CTA
+    // reports it and returns instead of computing on mis-swizzled tiles.
+    extern __shared__ __align__(1024) uint8_t smem_raw[];
+    uint8_t* smem = smem_raw;
+    if (smem_u32(smem_raw) & 1023u) {
+        if (threadIdx.x == 0) atomicCAS(&p.status->code, ST_OK, ST_SMEM_MISALIGNED);
+        return;
+    }
     const SmemPlan L = smem_plan(BMP, S, KC, SPC);
     uint8_t* hq = smem + L.hq;                                        // fp8 intermediate [SPC][BMP][128], swizzled
     float* xs = reinterpret_cast<float*>(smem + L.xs);                // [KC][BMP] token scales
@@ -134,7 +134,7 @@ fused_moe_w8a8_up_down_sm100_kernel(const __grid_constant__ CUtensorMap tm_w,
     float* topkw = reinterpret_cast<float*>(smem + L.topkw);          // [BMP]
     float* tokscale = reinterpret_cast<float*>(smem + L.tokscale);    // [SPC][BMP] s_h * topk_weight * scaling
     uint32_t* amax_part = reinterpret_cast<uint32_t*>(smem + L.amax); // [BMP][4] per-warp |h| maxima
-    uint64_t* full = reinterpret_cast<uint64_t*>(smem + L.bars);      // slot filled: TMA bytes + 2 gather warps
+    uint64_t* full = reinterpret_cast<uint64_t*>(smem + L.bars);      // slot filled: TMA bytes + 64 gather threads
     uint64_t* empty = full + S;                                       // slot free again
     uint64_t* acc_full = empty + S;
     uint64_t* acc_empty = acc_full + 2;
@@ -145,7 +145,7 @@ fused_moe_w8a8_up_down_sm100_kernel(const __grid_constant__ CUtensorMap tm_w,
 
     if (threadIdx.x == W_G0 * 32) {
         for (int i = 0; i < S; ++i) {
-            mbar_init(&full[i], 3);
+            mbar_init(&full[i], 1 + 64);
             mbar_init(&empty[i], 1);
         }
         for (int i = 0; i < 2; ++i) {
@@ -207,6 +207,7 @@ fused_moe_w8a8_up_down_sm100_kernel(const __grid_constant__ CUtensorMap tm_w,
                 if (!mbar_wait(&acc_empty[b], aph ^ 1, abort_flag, p.status, 21, it)) break;
                 AMOE_STAMP(9, it);
                 if (!mbar_wait(&full[s], ph, abort_flag, p.status, 22, it)) break;
+                fence_proxy_async_smem();      // token rows were written by cp.async, the UMMA reads them through the async proxy
                 tc_fence_after();
                 AMOE_STAMP(1, it);
                 const uint64_t off = static_cast<uint64_t>(s * dstep);
@@ -251,9 +252,8 @@ fused_moe_w8a8_up_down_sm100_kernel(const __grid_constant__ CUtensorMap tm_w,
             prefetch_tmap(&tm_w2);
         }
         const uint32_t dst0 = row0 * 128 + ((ch ^ (row0 & 7)) << 4);   // + i*1024 for piece i (row & 7 unchanged)
-        const int lag = p.lag;
         bool ok = true;
-        int s = 0, sl_sig = 0;                      // slot being filled / slot whose completion is signalled next
+        int s = 0;                                  // ring slot being filled
         uint32_t ph = 0;
         int kc = 0, sl = 0;
         for (int it = 0; it < UPI; ++it) {
@@ -274,30 +274,14 @@ fused_moe_w8a8_up_down_sm100_kernel(const __grid_constant__ CUtensorMap tm_w,
                 const uint8_t* src = v ? col + (static_cast<size_t>(src16[i]) << 4) : p.x;
                 cp_async_16(base + i * 1024, src, v ? 16u : 0u);
             }
-            cp_async_commit();
-            if (it >= lag) {
-                cp_async_wait_dyn(lag);
-                fence_proxy_async_smem();
-                __syncwarp();
-                if (lane == 0) mbar_arrive(&full[sl_sig]);
-                if (++sl_sig == S) sl_sig = 0;
-            }
+            cp_async_mbar_arrive_noinc(&full[s]);      // arrives when this thread's copies have landed
             if (++s == S) { s = 0; ph ^= 1; }
             if (++kc == KC) { kc = 0; ++sl; }
         }
-        cp_async_wait<0>();
-        if (ok) {
-            fence_proxy_async_smem();
-            __syncwarp();
-            if (lane == 0)
-                for (int it = max(UPI - lag, 0); it < UPI; ++it) {
-                    mbar_arrive(&full[sl_sig]);
-                    if (++sl_sig == S) sl_sig = 0;
-                }
-        }
+        cp_async_wait_all();                        // nothing of this thread may still be in flight at exit
         if (tma_thread && ok) {
             // down phase: this thread keeps feeding w2 tiles; there is no token gather any more, so it
-            // also stands in for the two gather warps on the slot's barrier (count 3)
+            // also stands in for the 64 gather threads on the slot's barrier
             for (int jt = 0; jt < ND; ++jt) {
                 const int it = UPI + jt;
                 AMOE_STAMP(7, it);
@@ -312,8 +296,7 @@ fused_moe_w8a8_up_down_sm100_kernel(const __grid_constant__ CUtensorMap tm_w,
                     tma_load_3d(st, &tm_w2, &full[s], slice0 * 128, jt * 128, expert);
                     tma_load_3d(st + kTileBytes, &tm_w2, &full[s], (slice0 + 1) * 128, jt * 128, expert);
                 }
-                mbar_arrive(&full[s]);
-                mbar_arrive(&full[s]);
+                mbar_arrive_n(&full[s], 64);
                 if (++s == S) { s = 0; ph ^= 1; }
             }
         }

@@ -18,6 +18,7 @@
 
 #include "../../include/alpha_moe_b200.h"
 #include "fused_moe_kernel.cuh"
+#include "fused_moe_kernel_tm.cuh"
 
 namespace {
 
@@ -119,13 +120,17 @@ constexpr int kMaxDynSmem = 232448;  // 227 KB opt-in limit per CTA on sm_100
 
 int padded_block_m(int block_m) { return block_m <= 16 ? 16 : block_m <= 32 ? 32 : block_m <= 64 ? 64 : 128; }
 
+// Blocks of more than 64 assignments run the token-major kernel (tokens on the TMEM lanes).
+bool token_major(int block_m) { return block_m > 64; }
+
 // Ring depth = the `stages` knob, lowered until the plan fits in shared memory.
 int plan(int K, int block_m, int stages, int spc, int* depth, int* bmp, int* smem_bytes) {
     const int kc = K / 128;
     const int b = padded_block_m(block_m);
     int s = stages;
     for (; s >= 1; --s) {
-        const int need = static_cast<int>(amoe::smem_plan(b, s, kc, spc).total) + 1024;
+        const int need = static_cast<int>(token_major(block_m) ? amoe::smem_plan_tm(s, kc, spc).total
+                                                               : amoe::smem_plan(b, s, kc, spc).total);
         if (need <= kMaxDynSmem) {
             *depth = s;
             *bmp = b;
@@ -149,6 +154,22 @@ int launch_variant(const CUtensorMap& mw, const CUtensorMap& mw2, const amoe::Mo
     }
     constexpr int threads = 128 * (BMP >= 64 ? 2 : 1) + 128;
     kern<<<grid, threads, smem_bytes, stream>>>(mw, mw2, p);
+    CUDA_TRY(cudaGetLastError());
+    return ALPHA_MOE_OK;
+}
+
+template <int SPC>
+int launch_tokmajor(const CUtensorMap& mw, const CUtensorMap& mw2, const amoe::MoeParams& p, int grid, int smem_bytes,
+                    cudaStream_t stream) {
+    auto kern = amoe::fused_moe_w8a8_up_down_sm100_tokmajor_kernel<SPC>;
+    static int configured_smem[64] = {0};
+    int dev = 0;
+    CUDA_TRY(cudaGetDevice(&dev));
+    if (dev < 64 && configured_smem[dev] < smem_bytes) {
+        CUDA_TRY(cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, kMaxDynSmem));
+        configured_smem[dev] = kMaxDynSmem;
+    }
+    kern<<<grid, 384, smem_bytes, stream>>>(mw, mw2, p);
     CUDA_TRY(cudaGetLastError());
     return ALPHA_MOE_OK;
 }
@@ -213,7 +234,6 @@ int alpha_moe_b200_fused_moe_w8a8_up_down(const void* x, const float* x_scale, c
     p.sorted_num = sorted_num;
     p.block_m = block_m;
     p.stages = depth;
-    p.lag = depth - 1 < 2 ? depth - 1 : 2;
     p.scaling = scaling_factor;
     p.status = status;
 #ifdef AMOE_TRACE
@@ -226,6 +246,10 @@ int alpha_moe_b200_fused_moe_w8a8_up_down(const void* x, const float* x_scale, c
     if (grid > 0x7FFFFFFFLL) return fail(ALPHA_MOE_E_ARG, "grid too large");
     cudaStream_t st = static_cast<cudaStream_t>(stream);
     const int g = static_cast<int>(grid);
+    if (token_major(block_m)) {
+        return spc == 1 ? launch_tokmajor<1>(maps->w, maps->w2, p, g, smem_bytes, st)
+                        : launch_tokmajor<2>(maps->w, maps->w2, p, g, smem_bytes, st);
+    }
     if (spc == 1) {
         switch (bmp) {
             case 16: return launch_variant<16, 1>(maps->w, maps->w2, p, g, smem_bytes, st);

@@ -25,7 +25,7 @@ struct KernelStatus {
     int where;    // role-specific tag (which barrier)
     int iter;     // pipeline iteration
 };
-enum : int { ST_OK = 0, ST_WAIT_TIMEOUT = 1 };
+enum : int { ST_OK = 0, ST_WAIT_TIMEOUT = 1, ST_SMEM_MISALIGNED = 2 };
 
 __device__ __forceinline__ uint32_t smem_u32(const void* p) {
     return static_cast<uint32_t>(__cvta_generic_to_shared(p));
@@ -111,6 +111,16 @@ __device__ __forceinline__ void tma_load_3d(void* dst, const CUtensorMap* m, uin
 __device__ __forceinline__ void cp_async_16(uint32_t dst_smem, const void* src, uint32_t src_bytes) {
     asm volatile("cp.async.cg.shared.global [%0], [%1], 16, %2;" ::"r"(dst_smem), "l"(src), "r"(src_bytes) : "memory");
 }
+// The mbarrier receives one arrival from this thread once all cp.async copies it has issued so far have
+// landed (asynchronously: the thread does not wait).  .noinc: the arrival is part of the barrier's
+// expected count, so a phase cannot complete before every gathering thread's copies are in.
+__device__ __forceinline__ void cp_async_mbar_arrive_noinc(uint64_t* bar) {
+    asm volatile("cp.async.mbarrier.arrive.noinc.shared::cta.b64 [%0];" ::"r"(smem_u32(bar)) : "memory");
+}
+__device__ __forceinline__ void mbar_arrive_n(uint64_t* bar, uint32_t n) {
+    asm volatile("mbarrier.arrive.shared::cta.b64 _, [%0], %1;" ::"r"(smem_u32(bar)), "r"(n) : "memory");
+}
+__device__ __forceinline__ void cp_async_wait_all() { asm volatile("cp.async.wait_all;" ::: "memory"); }
 __device__ __forceinline__ void cp_async_commit() { asm volatile("cp.async.commit_group;" ::: "memory"); }
 template <int N>
 __device__ __forceinline__ void cp_async_wait() {

@@ -47,7 +47,9 @@ def best_knobs(m: int):
         return 16, 32, 8, 5
     if m <= 256:
         return 16, 32, 8, 3
-    return 64, 64, 4, 5
+    if m <= 1024:
+        return 64, 64, 4, 5
+    return 128, 64, 4, 3
 
 
 def load_peaks():

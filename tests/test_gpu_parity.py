@@ -53,8 +53,9 @@ def test_deepseek_shard_shape_small_expert_count(m):
         if m < bm and bm != 16:
             continue
         ref = orc.run_oracle(case, bm)
-        got = run_capi(case, bm, 32, 8, st, dcase=dcase)
-        check_close(got, ref, tag=f"ds16 M={m} bm={bm}")
+        for bn, wn in ((32, 8), (64, 4)):      # one / two intermediate slices per CTA
+            got = run_capi(case, bm, bn, wn, st, dcase=dcase)
+            check_close(got, ref, tag=f"ds16 M={m} bm={bm} bn={bn}")
 
 
 test_deepseek_shard_shape_small_expert_count.weights = None
@@ -74,7 +75,9 @@ def _ds_weights():
     (8, 384, 128, 40, 3, 24),        # odd number of K chunks: last w2 slot is half empty
     (4, 256, 512, 17, 2, 16),        # four intermediate slices
     (37, 4096, 256, 32, 9, 32),      # reference sweep shape (E=37, K=4096)
-    (8, 1280, 384, 64, 4, 128),      # three slices, widest tile
+    (8, 1280, 384, 64, 4, 128),      # three slices, token-major kernel
+    (8, 1024, 512, 200, 4, 128),     # token-major kernel, two slices per CTA
+    (8, 1024, 512, 200, 4, 96),      # same, blocks only three quarters full
 ])
 def test_shapes(e, k, inter, m, top_k, bm):
     case = orc.make_case(e, k, inter, m, top_k, seed=e + k + m, scaling=1.0)
