@@ -27,6 +27,12 @@ lib.alpha_moe_b200_read_status.restype = _i
 lib.alpha_moe_b200_read_status.argtypes = [ctypes.POINTER(ctypes.c_int32), _i]
 lib.alpha_moe_b200_plan.restype = _i
 lib.alpha_moe_b200_plan.argtypes = [_i, _i, _i, _i, ctypes.POINTER(ctypes.c_int32)]
+lib.alpha_moe_b200_moe_align_block_size.restype = _i
+lib.alpha_moe_b200_moe_align_block_size.argtypes = [_vp, _i, _i, _i, _vp, _vp, _vp, _vp, _vp]
+lib.alpha_moe_b200_align_workspace_bytes.restype = ctypes.c_int64
+lib.alpha_moe_b200_align_workspace_bytes.argtypes = [_i, _i]
+lib.alpha_moe_b200_per_token_group_quant_fp8.restype = _i
+lib.alpha_moe_b200_per_token_group_quant_fp8.argtypes = [_vp, _vp, _vp, _i, _i, _i, _vp]
 lib.alpha_moe_b200_last_error.restype = ctypes.c_char_p
 lib.alpha_moe_b200_version.restype = ctypes.c_char_p
 
@@ -52,6 +58,22 @@ def fused_moe_w8a8_up_down(x, x_scale, w, w_scale, w2, w2_scale, out, sorted_tok
         x, x_scale, w, w_scale, w2, w2_scale, out, sorted_token_ids, expert_ids,
         num_tokens_post_padded, topk_weights, top_k, M, K, N, num_experts, sorted_num,
         block_m, block_n, warp_n, stages, scaling_factor, stream))
+
+
+def moe_align_block_size(topk_ids, numel, num_experts, block_m, sorted_token_ids, expert_ids,
+                         num_tokens_post_padded, workspace=0, stream=0) -> None:
+    """Raw call: device addresses (ints); workspace of align_workspace_bytes(numel, num_experts) bytes."""
+    _check(lib.alpha_moe_b200_moe_align_block_size(topk_ids, numel, num_experts, block_m, sorted_token_ids,
+                                                   expert_ids, num_tokens_post_padded, workspace or None, stream))
+
+
+def align_workspace_bytes(numel: int, num_experts: int) -> int:
+    return int(lib.alpha_moe_b200_align_workspace_bytes(numel, num_experts))
+
+
+def per_token_group_quant_fp8(x_bf16, x_fp8, x_scale, M, K, zero_src=False, stream=0) -> None:
+    """Raw call: device addresses (ints)."""
+    _check(lib.alpha_moe_b200_per_token_group_quant_fp8(x_bf16, x_fp8, x_scale, M, K, int(zero_src), stream))
 
 
 def read_status(reset: bool = False):

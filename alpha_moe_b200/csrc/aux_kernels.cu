@@ -1,0 +1,278 @@
+// The two kernels a serving engine runs immediately before the fused MoE operator, which the
+// reference imports from SGLang (jit_moe.py:142,158; extra/sglang.patch:30-35):
+//   * moe_align_block_size  - block schedule (sorted_token_ids, expert_ids, num_tokens_post_padded)
+//   * per-token-group fp8 quantisation of the activations (group = 128), optionally zeroing the
+//     bf16 source afterwards, which is what the call site does next (extra/sglang.patch:31).
+// Both are integer / byte work bound by memory traffic; no tensor cores involved.
+#include <cuda_bf16.h>
+#include <cuda_fp8.h>
+#include <cuda_runtime.h>
+#include <stdint.h>
+
+#include "../../include/alpha_moe_b200.h"
+#include "capi_internal.h"
+
+namespace amoe_aux {
+
+using amoe_capi::fail;
+
+#define AUX_TRY(expr)                                                                              \
+    do {                                                                                           \
+        cudaError_t err__ = (expr);                                                                \
+        if (err__ != cudaSuccess)                                                                  \
+            return fail(ALPHA_MOE_E_CUDA, "%s failed: %s", #expr, cudaGetErrorString(err__));      \
+    } while (0)
+
+// ------------------------------------------------------------------------------------------------
+// moe_align_block_size.  Flat assignment index p = token * top_k + j, expert topk_ids[p].
+// Each expert's indices are written in ascending order (a stable counting sort), starting at a
+// multiple of `block`, the rest of the expert's last block holding the sentinel `numel`.
+//
+// Work is cut into chunks of kChunk consecutive assignments, one CTA each:
+//   pass 1  fill outputs with their defaults; per-chunk histogram -> hist[chunk][expert]
+//   pass 2  (one CTA) padded expert sizes, their exclusive scan, per-chunk start offsets,
+//           expert_ids per block, num_tokens_post_padded
+//   pass 3  stable scatter: warps walk their 128 assignments in order, ranking equal experts
+//           inside a warp round with match.any
+// When everything fits one chunk the three passes run inside one CTA of one launch.
+constexpr int kChunk = 1024;          // assignments per CTA (8 warps x 4 rounds x 32 lanes)
+constexpr int kAlignThreads = 256;
+constexpr int kMaxExperts = 1024;     // per-warp counters live in shared memory: 8 x E ints
+
+// Per-warp counts of each expert over the warp's 128 consecutive assignments of the chunk.
+__device__ __forceinline__ void count_chunk(const int32_t* ids, int numel, int chunk_start, int E, int* cnt /*[8][E]*/) {
+    const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
+    for (int i = threadIdx.x; i < 8 * E; i += kAlignThreads) cnt[i] = 0;
+    __syncthreads();
+#pragma unroll
+    for (int r = 0; r < 4; ++r) {
+        const int p = chunk_start + warp * 128 + r * 32 + lane;
+        const bool in = p < numel;
+        int e = in ? ids[p] : -1;
+        if (e < 0 || e >= E) e = -1;                       // ids outside [0,E) are ignored
+        const unsigned same = __match_any_sync(0xFFFFFFFFu, e);
+        if (e >= 0 && (same & ((1u << lane) - 1)) == 0) cnt[warp * E + e] += __popc(same);   // leader lane
+        __syncwarp();
+    }
+    __syncthreads();
+}
+
+// Stable scatter of one chunk.  base[w][e] = first output slot for warp w's assignments of expert e.
+__device__ __forceinline__ void scatter_chunk(const int32_t* ids, int numel, int chunk_start, int E, int* base,
+                                              int32_t* sorted) {
+    const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
+#pragma unroll
+    for (int r = 0; r < 4; ++r) {
+        const int p = chunk_start + warp * 128 + r * 32 + lane;
+        const bool in = p < numel;
+        int e = in ? ids[p] : -1;
+        if (e < 0 || e >= E) e = -1;
+        const unsigned same = __match_any_sync(0xFFFFFFFFu, e);
+        const int leader = __ffs(same) - 1;
+        int pos0 = 0;
+        if (e >= 0 && lane == leader) {
+            pos0 = base[warp * E + e];
+            base[warp * E + e] = pos0 + __popc(same);
+        }
+        pos0 = __shfl_sync(0xFFFFFFFFu, pos0, leader);
+        if (e >= 0) sorted[pos0 + __popc(same & ((1u << lane) - 1))] = p;
+        __syncwarp();
+    }
+}
+
+__global__ void __launch_bounds__(kAlignThreads)
+moe_align_pass1_kernel(const int32_t* ids, int numel, int E, int block, int32_t* sorted, int sorted_len,
+                       int32_t* expert_ids, int n_blocks_max, int* hist /*[chunks][E]*/) {
+    __shared__ int cnt[8 * kMaxExperts];
+    const int gtid = blockIdx.x * kAlignThreads + threadIdx.x, gsz = gridDim.x * kAlignThreads;
+    for (int i = gtid; i < sorted_len; i += gsz) sorted[i] = numel;
+    for (int i = gtid; i < n_blocks_max; i += gsz) expert_ids[i] = 0;
+    count_chunk(ids, numel, blockIdx.x * kChunk, E, cnt);
+    for (int e = threadIdx.x; e < E; e += kAlignThreads) {
+        int s = 0;
+#pragma unroll
+        for (int w = 0; w < 8; ++w) s += cnt[w * E + e];
+        hist[blockIdx.x * E + e] = s;
+    }
+}
+
+// One CTA.  On exit hist[c][e] holds the first output slot of chunk c's assignments of expert e.
+__global__ void __launch_bounds__(1024)
+moe_align_pass2_kernel(int* hist, int chunks, int E, int block, int32_t* expert_ids, int32_t* num_post_pad) {
+    __shared__ int padded[kMaxExperts];
+    __shared__ int start[kMaxExperts + 1];
+    for (int e = threadIdx.x; e < E; e += blockDim.x) {
+        int tot = 0;
+        for (int c = 0; c < chunks; ++c) tot += hist[c * E + e];
+        padded[e] = (tot + block - 1) / block * block;
+    }
+    __syncthreads();
+    if (threadIdx.x == 0) {
+        int run = 0;
+        for (int e = 0; e < E; ++e) {
+            start[e] = run;
+            run += padded[e];
+        }
+        start[E] = run;
+        num_post_pad[0] = run;
+    }
+    __syncthreads();
+    for (int e = threadIdx.x; e < E; e += blockDim.x) {
+        int run = start[e];
+        for (int c = 0; c < chunks; ++c) {
+            const int n = hist[c * E + e];
+            hist[c * E + e] = run;
+            run += n;
+        }
+        for (int b = start[e] / block; b < start[e + 1] / block; ++b) expert_ids[b] = e;
+    }
+}
+
+__global__ void __launch_bounds__(kAlignThreads)
+moe_align_pass3_kernel(const int32_t* ids, int numel, int E, const int* hist, int32_t* sorted) {
+    __shared__ int cnt[8 * kMaxExperts];
+    count_chunk(ids, numel, blockIdx.x * kChunk, E, cnt);
+    for (int e = threadIdx.x; e < E; e += kAlignThreads) {     // counts -> exclusive prefix over the 8 warps
+        int run = hist[blockIdx.x * E + e];
+#pragma unroll
+        for (int w = 0; w < 8; ++w) {
+            const int n = cnt[w * E + e];
+            cnt[w * E + e] = run;
+            run += n;
+        }
+    }
+    __syncthreads();
+    scatter_chunk(ids, numel, blockIdx.x * kChunk, E, cnt, sorted);
+}
+
+// Everything in one CTA when there is a single chunk (numel <= kChunk: e.g. up to 113 tokens at top_k = 9).
+__global__ void __launch_bounds__(kAlignThreads)
+moe_align_single_kernel(const int32_t* ids, int numel, int E, int block, int32_t* sorted, int sorted_len,
+                        int32_t* expert_ids, int n_blocks_max, int32_t* num_post_pad) {
+    __shared__ int cnt[8 * kMaxExperts];
+    __shared__ int start[kMaxExperts + 1];
+    for (int i = threadIdx.x; i < sorted_len; i += kAlignThreads) sorted[i] = numel;
+    for (int i = threadIdx.x; i < n_blocks_max; i += kAlignThreads) expert_ids[i] = 0;
+    count_chunk(ids, numel, 0, E, cnt);
+    for (int e = threadIdx.x; e < E; e += kAlignThreads) {
+        int s = 0;
+#pragma unroll
+        for (int w = 0; w < 8; ++w) s += cnt[w * E + e];
+        start[e] = (s + block - 1) / block * block;            // padded size for now
+    }
+    __syncthreads();
+    if (threadIdx.x == 0) {
+        int run = 0;
+        for (int e = 0; e < E; ++e) {
+            const int n = start[e];
+            start[e] = run;
+            run += n;
+        }
+        start[E] = run;
+        num_post_pad[0] = run;
+    }
+    __syncthreads();                                            // also orders the default fills above before the writes below
+    for (int e = threadIdx.x; e < E; e += kAlignThreads) {
+        int run = start[e];
+#pragma unroll
+        for (int w = 0; w < 8; ++w) {
+            const int n = cnt[w * E + e];
+            cnt[w * E + e] = run;
+            run += n;
+        }
+        for (int b = start[e] / block; b < start[e + 1] / block; ++b) expert_ids[b] = e;
+    }
+    __syncthreads();
+    scatter_chunk(ids, numel, 0, E, cnt, sorted);
+}
+
+// ------------------------------------------------------------------------------------------------
+// Per-(token, 128-group) fp8 quantisation: scale = max(amax, 1e-10) / 448, q = e4m3_rn(clamp(x / scale)).
+// One warp per group: 4 bf16 per lane in, 4 fp8 per lane out; algorithmic traffic 3 bytes per element
+// (+ 2 when the source is zeroed).  IEEE divisions keep the result bit-identical to the CPU restatement.
+__global__ void __launch_bounds__(256)
+group_quant_fp8_kernel(__nv_bfloat16* x, uint8_t* q, float* scale, long long n_groups, int zero_src) {
+    const long long g = static_cast<long long>(blockIdx.x) * 8 + (threadIdx.x >> 5);
+    if (g >= n_groups) return;
+    const int lane = threadIdx.x & 31;
+    uint2* src = reinterpret_cast<uint2*>(x + g * 128) + lane;
+    const uint2 raw = *src;
+    const __nv_bfloat162 a = *reinterpret_cast<const __nv_bfloat162*>(&raw.x);
+    const __nv_bfloat162 b = *reinterpret_cast<const __nv_bfloat162*>(&raw.y);
+    const float v[4] = {__low2float(a), __high2float(a), __low2float(b), __high2float(b)};
+    float amax = fmaxf(fmaxf(fabsf(v[0]), fabsf(v[1])), fmaxf(fabsf(v[2]), fabsf(v[3])));
+#pragma unroll
+    for (int o = 16; o > 0; o >>= 1) amax = fmaxf(amax, __shfl_xor_sync(0xFFFFFFFFu, amax, o));
+    const float s = __fdiv_rn(fmaxf(amax, 1e-10f), 448.0f);
+    uint32_t packed = 0;
+#pragma unroll
+    for (int i = 0; i < 4; ++i) {
+        const float y = fminf(fmaxf(__fdiv_rn(v[i], s), -448.0f), 448.0f);
+        packed |= static_cast<uint32_t>(__nv_cvt_float_to_fp8(y, __NV_SATFINITE, __NV_E4M3)) << (8 * i);
+    }
+    reinterpret_cast<uint32_t*>(q + g * 128)[lane] = packed;
+    if (lane == 0) scale[g] = s;
+    if (zero_src) *src = make_uint2(0u, 0u);
+}
+
+}  // namespace amoe_aux
+
+extern "C" {
+
+int64_t alpha_moe_b200_align_workspace_bytes(int numel, int num_experts) {
+    if (numel <= 0 || num_experts <= 0) return 0;
+    const int64_t chunks = (static_cast<int64_t>(numel) + amoe_aux::kChunk - 1) / amoe_aux::kChunk;
+    return chunks <= 1 ? 0 : chunks * num_experts * static_cast<int64_t>(sizeof(int));
+}
+
+int alpha_moe_b200_moe_align_block_size(const int32_t* topk_ids, int numel, int num_experts, int block_m,
+                                        int32_t* sorted_token_ids, int32_t* expert_ids,
+                                        int32_t* num_tokens_post_padded, void* workspace, void* stream) {
+    using namespace amoe_aux;
+    if (!topk_ids || !sorted_token_ids || !expert_ids || !num_tokens_post_padded)
+        return fail(ALPHA_MOE_E_ARG, "null pointer argument");
+    if (numel <= 0) return fail(ALPHA_MOE_E_ARG, "numel must be positive (got %d)", numel);
+    if (num_experts <= 0 || num_experts > kMaxExperts)
+        return fail(ALPHA_MOE_E_ARG, "num_experts must be in 1..%d (got %d)", kMaxExperts, num_experts);
+    if (block_m <= 0) return fail(ALPHA_MOE_E_ARG, "block_m must be positive (got %d)", block_m);
+    const long long sorted_len = static_cast<long long>(numel) + static_cast<long long>(num_experts) * (block_m - 1);
+    if (sorted_len > 0x7FFFFFFFLL) return fail(ALPHA_MOE_E_ARG, "schedule too long for int32 indices");
+    const int n_blocks_max = static_cast<int>((sorted_len + block_m - 1) / block_m);
+    const int chunks = (numel + kChunk - 1) / kChunk;
+    cudaStream_t st = static_cast<cudaStream_t>(stream);
+    if (chunks == 1) {
+        moe_align_single_kernel<<<1, kAlignThreads, 0, st>>>(topk_ids, numel, num_experts, block_m, sorted_token_ids,
+                                                            static_cast<int>(sorted_len), expert_ids, n_blocks_max,
+                                                            num_tokens_post_padded);
+        AUX_TRY(cudaGetLastError());
+        return ALPHA_MOE_OK;
+    }
+    if (!workspace) return fail(ALPHA_MOE_E_ARG, "workspace is required for more than %d assignments", kChunk);
+    int* hist = static_cast<int*>(workspace);
+    moe_align_pass1_kernel<<<chunks, kAlignThreads, 0, st>>>(topk_ids, numel, num_experts, block_m, sorted_token_ids,
+                                                            static_cast<int>(sorted_len), expert_ids, n_blocks_max, hist);
+    AUX_TRY(cudaGetLastError());
+    moe_align_pass2_kernel<<<1, 1024, 0, st>>>(hist, chunks, num_experts, block_m, expert_ids, num_tokens_post_padded);
+    AUX_TRY(cudaGetLastError());
+    moe_align_pass3_kernel<<<chunks, kAlignThreads, 0, st>>>(topk_ids, numel, num_experts, hist, sorted_token_ids);
+    AUX_TRY(cudaGetLastError());
+    return ALPHA_MOE_OK;
+}
+
+int alpha_moe_b200_per_token_group_quant_fp8(void* x_bf16, void* x_fp8, float* x_scale, int M, int K, int zero_src,
+                                             void* stream) {
+    using namespace amoe_aux;
+    if (!x_bf16 || !x_fp8 || !x_scale) return fail(ALPHA_MOE_E_ARG, "null pointer argument");
+    if (M <= 0 || K <= 0 || K % 128 != 0) return fail(ALPHA_MOE_E_ARG, "need M > 0 and K a positive multiple of 128");
+    if ((reinterpret_cast<uintptr_t>(x_bf16) & 7) || (reinterpret_cast<uintptr_t>(x_fp8) & 3))
+        return fail(ALPHA_MOE_E_ARG, "x_bf16 must be 8-byte aligned and x_fp8 4-byte aligned");
+    const long long n_groups = static_cast<long long>(M) * (K / 128);
+    const long long blocks = (n_groups + 7) / 8;
+    if (blocks > 0x7FFFFFFFLL) return fail(ALPHA_MOE_E_ARG, "too many groups");
+    group_quant_fp8_kernel<<<static_cast<unsigned>(blocks), 256, 0, static_cast<cudaStream_t>(stream)>>>(
+        static_cast<__nv_bfloat16*>(x_bf16), static_cast<uint8_t*>(x_fp8), x_scale, n_groups, zero_src);
+    AUX_TRY(cudaGetLastError());
+    return ALPHA_MOE_OK;
+}
+
+}  // extern "C"

@@ -17,6 +17,7 @@
 #include <tuple>
 
 #include "../../include/alpha_moe_b200.h"
+#include "capi_internal.h"
 #include "fused_moe_kernel.cuh"
 #include "fused_moe_kernel_tm.cuh"
 
@@ -24,6 +25,9 @@ namespace {
 
 thread_local std::string g_last_error;
 
+}  // namespace
+
+namespace amoe_capi {
 int fail(int code, const char* fmt, ...) {
     char buf[512];
     va_list ap;
@@ -33,6 +37,10 @@ int fail(int code, const char* fmt, ...) {
     g_last_error = buf;
     return code;
 }
+}  // namespace amoe_capi
+
+namespace {
+using amoe_capi::fail;
 
 #define CUDA_TRY(expr)                                                                             \
     do {                                                                                           \

@@ -43,6 +43,26 @@ int alpha_moe_b200_fused_moe_w8a8_up_down(
     int num_experts, int sorted_num, int block_m, int block_n, int warp_n, int stages,
     float scaling_factor, void* stream);
 
+/* Replaces the external moe_align_block_size the reference calls before the operator
+ * (jit_moe.py:158, extra/sglang.patch:33-35).  topk_ids [numel] i32 (the flattened [M,top_k] expert
+ * ids; ids outside [0,num_experts) are ignored).  Outputs: sorted_token_ids
+ * [numel + num_experts*(block_m-1)] - each expert's flat indices in ascending order, starting at a
+ * multiple of block_m, unused slots = numel; expert_ids [ceil(that length / block_m)] - expert of each
+ * used block, 0 for unused ones; num_tokens_post_padded [1].  num_experts <= 1024.
+ * workspace: device scratch of alpha_moe_b200_align_workspace_bytes(numel, num_experts) bytes
+ * (0 - and workspace may be NULL - when numel <= 1024). */
+int alpha_moe_b200_moe_align_block_size(const int32_t* topk_ids, int numel, int num_experts, int block_m,
+                                        int32_t* sorted_token_ids, int32_t* expert_ids,
+                                        int32_t* num_tokens_post_padded, void* workspace, void* stream);
+int64_t alpha_moe_b200_align_workspace_bytes(int numel, int num_experts);
+
+/* Replaces the external sglang_per_token_group_quant_fp8(x, 128) the reference calls before the
+ * operator (jit_moe.py:142, extra/sglang.patch:30): bf16 [M,K] -> fp8 e4m3 [M,K] + f32 scale [M,K/128],
+ * scale = max(amax,1e-10)/448.  If zero_src != 0 the bf16 source is zeroed after it has been read,
+ * which is what the call site does next (extra/sglang.patch:31) because `out` aliases it. */
+int alpha_moe_b200_per_token_group_quant_fp8(void* x_bf16, void* x_fp8, float* x_scale, int M, int K,
+                                             int zero_src, void* stream);
+
 /* Reads (and optionally clears) the status word of the current device: out4 = {code, block, where, iter};
  * code 0 means no kernel wait has ever run out.  Synchronises the device. */
 int alpha_moe_b200_read_status(int32_t* out4, int reset);

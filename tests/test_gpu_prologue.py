@@ -1,0 +1,87 @@
+"""GPU tests of the two pre-operator kernels, bit-exact against the CPU restatement (integer and
+byte work): block schedule and per-token-group fp8 quantisation, then the whole call-site sequence
+of extra/sglang.patch:25-41 end to end."""
+import pytest
+import torch
+
+from oracle import moe_oracle as orc
+
+pytestmark = pytest.mark.gpu
+
+
+@pytest.mark.parametrize("m,e,k,block", [(1, 257, 9, 16), (4, 8, 2, 8), (16, 8, 2, 16), (64, 257, 9, 8),
+                                         (113, 257, 9, 16), (114, 257, 9, 16), (300, 37, 9, 32),
+                                         (1024, 512, 10, 64), (4096, 257, 9, 128), (8192, 257, 9, 72)])
+def test_moe_align_block_size_matches_oracle_exactly(m, e, k, block):
+    from alpha_moe_b200.prologue import moe_align_block_size
+    g = torch.Generator().manual_seed(m + e)
+    ids, _ = orc.route_topk(torch.randn(m, e, generator=g), k)
+    want = orc.moe_align_block_size(ids, block, e)
+    got = moe_align_block_size(ids.cuda(), block, e)
+    torch.cuda.synchronize()
+    for a, b, name in zip(got, want, ("sorted_token_ids", "expert_ids", "num_tokens_post_padded")):
+        assert torch.equal(a.cpu(), b), name
+
+
+def test_moe_align_duplicates_skew_and_out_of_range_ids():
+    from alpha_moe_b200.prologue import moe_align_block_size
+    g = torch.Generator().manual_seed(0)
+    # everything routed to two experts, duplicates inside a token (reference test generator draws with replacement)
+    ids = torch.randint(0, 2, (700, 9), generator=g, dtype=torch.int32) * 5
+    want = orc.moe_align_block_size(ids, 16, 8)
+    got = moe_align_block_size(ids.cuda(), 16, 8)
+    for a, b in zip(got, want):
+        assert torch.equal(a.cpu(), b)
+    # ids outside [0, E) are ignored (they never reach a block)
+    bad = ids.clone()
+    bad[::7, 0] = -1
+    bad[3::11, 1] = 8
+    sid, eid, npp = [t.cpu() for t in moe_align_block_size(bad.cuda(), 16, 8)]
+    flat = bad.reshape(-1)
+    live = sid[: int(npp)]
+    real = live[live < flat.numel()]
+    assert sorted(real.tolist()) == [i for i in range(flat.numel()) if 0 <= int(flat[i]) < 8]
+
+
+@pytest.mark.parametrize("m,k", [(1, 128), (3, 512), (64, 7168), (1000, 2048)])
+def test_group_quant_matches_oracle_bit_for_bit(m, k):
+    from alpha_moe_b200.prologue import per_token_group_quant_fp8
+    g = torch.Generator().manual_seed(m * 7 + k)
+    x = (torch.randn(m, k, generator=g) * torch.rand(m, 1, generator=g) * 3).to(torch.bfloat16)
+    x[0, :128] = 0                                     # an all-zero group: scale = 1e-10 / 448
+    if m > 2:
+        x[2, 5] = 300.0                                # an outlier
+    want_q, want_s = orc.quant_token_groups(x)
+    xd = x.cuda()
+    q, s = per_token_group_quant_fp8(xd)
+    torch.cuda.synchronize()
+    assert torch.equal(s.cpu(), want_s)
+    assert torch.equal(q.cpu().view(torch.uint8), want_q.view(torch.uint8))
+    assert torch.equal(xd.cpu(), x)                    # source untouched
+    q2, s2 = per_token_group_quant_fp8(xd, zero_input=True)
+    torch.cuda.synchronize()
+    assert torch.equal(q2.cpu().view(torch.uint8), want_q.view(torch.uint8)) and torch.equal(s2.cpu(), want_s)
+    assert (xd == 0).all()
+
+
+def test_call_site_sequence_end_to_end():
+    """quantise -> zero the activations -> schedule -> fused operator accumulating into the activation
+    buffer, exactly the sequence of the reference's call site (extra/sglang.patch:30-41)."""
+    import alpha_moe  # noqa: F401
+    from alpha_moe_b200.prologue import moe_align_block_size, sglang_per_token_group_quant_fp8
+    e, k, inter, m, top_k = 16, 1024, 256, 50, 4
+    g = torch.Generator().manual_seed(3)
+    w, w_scale, w2, w2_scale = orc.make_weights(e, k, inter, g)
+    hidden = torch.randn(m, k, generator=g).to(torch.bfloat16)
+    ids, wts = orc.route_topk(torch.randn(m, e, generator=g), top_k)
+    xq, xs = orc.quant_token_groups(hidden)
+    sid, eid, npp = orc.moe_align_block_size(ids, 16, e)
+    ref = orc.fused_moe_w8a8_up_down_oracle(xq, xs, w, w_scale, w2, w2_scale, sid, eid, npp, wts, top_k, 16, 2.5)
+
+    hs = hidden.cuda()
+    a, a_scale = sglang_per_token_group_quant_fp8(hs, 128, zero_input=True)
+    s_ids, e_ids, n_pad = moe_align_block_size(ids.cuda(), 16, e)
+    torch.ops.alpha_moe.fused_moe_w8a8_up_down(a, a_scale, w.cuda(), w_scale.cuda(), w2.cuda(), w2_scale.cuda(),
+                                               s_ids, e_ids, n_pad, wts.cuda(), hs, top_k, 16, 32, 8, 3, 2.5)
+    torch.cuda.synchronize()
+    assert orc.rel_l2(hs.cpu(), ref) <= 2e-2
