@@ -3,12 +3,13 @@
 Reference counterparts: alpha_moe_ops.py:28-88 (wrapper), alpha_moe_python/utils.py:5-29
 (interleave_tensor, get_best_config), csrc/torch_interface.cpp:105-127 (operator registration).
 
-Importing this package loads the C ABI library.  There is no CPU or eager fallback anywhere:
-if a shared object is missing the import (or load_torch_op) raises.
+There is no CPU or eager fallback anywhere: `alpha_moe_b200.capi` (the ctypes binding every
+entry point goes through) raises at import if libalpha_moe_b200.so is missing, and load_torch_op
+raises if the operator library is.  The package itself stays importable without them so that
+`python -m alpha_moe_b200.build` can create them.
 """
 from __future__ import annotations
 
-from . import capi                      # noqa: F401  (loads libalpha_moe_b200.so or raises)
 from .utils import interleave_tensor, get_best_config   # noqa: F401
 
 _torch_op_loaded = False
