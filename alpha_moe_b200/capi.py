@@ -29,6 +29,8 @@ lib.alpha_moe_b200_plan.restype = _i
 lib.alpha_moe_b200_plan.argtypes = [_i, _i, _i, _i, ctypes.POINTER(ctypes.c_int32)]
 lib.alpha_moe_b200_moe_align_block_size.restype = _i
 lib.alpha_moe_b200_moe_align_block_size.argtypes = [_vp, _i, _i, _i, _vp, _vp, _vp, _vp, _vp]
+lib.alpha_moe_b200_moe_align_block_size_noalloc.restype = _i
+lib.alpha_moe_b200_moe_align_block_size_noalloc.argtypes = [_vp, _i, _i, _i, _vp, _vp, _vp, _vp]
 lib.alpha_moe_b200_align_workspace_bytes.restype = ctypes.c_int64
 lib.alpha_moe_b200_align_workspace_bytes.argtypes = [_i, _i]
 lib.alpha_moe_b200_per_token_group_quant_fp8.restype = _i
@@ -65,6 +67,13 @@ def moe_align_block_size(topk_ids, numel, num_experts, block_m, sorted_token_ids
     """Raw call: device addresses (ints); workspace of align_workspace_bytes(numel, num_experts) bytes."""
     _check(lib.alpha_moe_b200_moe_align_block_size(topk_ids, numel, num_experts, block_m, sorted_token_ids,
                                                    expert_ids, num_tokens_post_padded, workspace or None, stream))
+
+
+def moe_align_block_size_noalloc(topk_ids, numel, num_experts, block_m, sorted_token_ids, expert_ids,
+                                 num_tokens_post_padded, stream=0) -> None:
+    """Raw call of the variant that uses the library's built-in scratch array (no workspace argument)."""
+    _check(lib.alpha_moe_b200_moe_align_block_size_noalloc(topk_ids, numel, num_experts, block_m, sorted_token_ids,
+                                                           expert_ids, num_tokens_post_padded, stream))
 
 
 def align_workspace_bytes(numel: int, num_experts: int) -> int:

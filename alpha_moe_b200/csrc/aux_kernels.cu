@@ -215,6 +215,11 @@ group_quant_fp8_kernel(__nv_bfloat16* x, uint8_t* q, float* scale, long long n_g
     if (zero_src) *src = make_uint2(0u, 0u);
 }
 
+// Scratch of the entry point that allocates nothing: the per-chunk histogram table lives here instead of
+// in a caller-provided workspace.  Every GPU that loads the library holds these 256 KB until exit.
+constexpr int kNoAllocScratchInts = 64 * 1024;
+static __device__ __align__(256) int g_align_scratch[kNoAllocScratchInts];
+
 }  // namespace amoe_aux
 
 extern "C" {
@@ -257,6 +262,33 @@ int alpha_moe_b200_moe_align_block_size(const int32_t* topk_ids, int numel, int 
     moe_align_pass3_kernel<<<chunks, kAlignThreads, 0, st>>>(topk_ids, numel, num_experts, hist, sorted_token_ids);
     AUX_TRY(cudaGetLastError());
     return ALPHA_MOE_OK;
+}
+
+int alpha_moe_b200_moe_align_block_size_noalloc(const int32_t* topk_ids, int numel, int num_experts, int block_m,
+                                                int32_t* sorted_token_ids, int32_t* expert_ids,
+                                                int32_t* num_tokens_post_padded, void* stream) {
+    using namespace amoe_aux;
+    if (numel <= 0 || num_experts <= 0) return fail(ALPHA_MOE_E_ARG, "numel and num_experts must be positive");
+    const long long chunks = (static_cast<long long>(numel) + kChunk - 1) / kChunk;
+    if (chunks > 1 && chunks * num_experts > kNoAllocScratchInts)
+        return fail(ALPHA_MOE_E_ARG,
+                    "problem too large for the built-in scratch: ceil(numel/%d) * num_experts = %lld exceeds %d; "
+                    "use alpha_moe_b200_moe_align_block_size with a caller-provided workspace",
+                    kChunk, chunks * num_experts, kNoAllocScratchInts);
+    // In host code the array's name is only a handle; the device address has to be asked for, once per
+    // device, with that device current.  This first call on a device should come before any stream capture.
+    static int* scratch_of_device[64] = {nullptr};
+    int dev = 0;
+    AUX_TRY(cudaGetDevice(&dev));
+    if (dev < 0 || dev >= 64) return fail(ALPHA_MOE_E_ARG, "device ordinal %d not supported", dev);
+    if (!scratch_of_device[dev]) {
+        int* ptr = nullptr;
+        AUX_TRY(cudaGetSymbolAddress(reinterpret_cast<void**>(&ptr), g_align_scratch));
+        scratch_of_device[dev] = ptr;
+    }
+    // Nothing in the scratch has to start at zero: pass 1 overwrites every [chunk][expert] entry this call reads.
+    return alpha_moe_b200_moe_align_block_size(topk_ids, numel, num_experts, block_m, sorted_token_ids, expert_ids,
+                                               num_tokens_post_padded, scratch_of_device[dev], stream);
 }
 
 int alpha_moe_b200_per_token_group_quant_fp8(void* x_bf16, void* x_fp8, float* x_scale, int M, int K, int zero_src,

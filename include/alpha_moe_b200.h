@@ -56,6 +56,21 @@ int alpha_moe_b200_moe_align_block_size(const int32_t* topk_ids, int numel, int 
                                         int32_t* num_tokens_post_padded, void* workspace, void* stream);
 int64_t alpha_moe_b200_align_workspace_bytes(int numel, int num_experts);
 
+/* No counterpart in the reference.  Same result as alpha_moe_b200_moe_align_block_size, for callers
+ * that must not allocate device memory around the call: code running inside a CUDA-graph capture or a
+ * serving loop with a frozen memory pool, plugins that are handed buffers but no allocator, and embedders
+ * whose device-memory budget is fixed at start-up.  The per-chunk histogram table lives in a 256 KB array
+ * compiled into the library (held by every GPU that loads it, until exit) instead of a workspace.
+ * Limit: ceil(numel/1024) * num_experts <= 65536 (e.g. 8192 tokens x top_k 9 with 257 experts uses 18504);
+ * larger problems are rejected with ALPHA_MOE_E_ARG.  The call itself performs no cudaMalloc / cudaFree and
+ * calls no allocating library routine.  The first call on each device looks up the array's device address;
+ * make that first call outside any stream capture.  All calls share the one array and nothing in it is
+ * assumed zero on entry, but two calls whose kernels overlap on the GPU (different streams, several host
+ * threads) race on it: serialise them. */
+int alpha_moe_b200_moe_align_block_size_noalloc(const int32_t* topk_ids, int numel, int num_experts, int block_m,
+                                                int32_t* sorted_token_ids, int32_t* expert_ids,
+                                                int32_t* num_tokens_post_padded, void* stream);
+
 /* Replaces the external sglang_per_token_group_quant_fp8(x, 128) the reference calls before the
  * operator (jit_moe.py:142, extra/sglang.patch:30): bf16 [M,K] -> fp8 e4m3 [M,K] + f32 scale [M,K/128],
  * scale = max(amax,1e-10)/448.  If zero_src != 0 the bf16 source is zeroed after it has been read,
