@@ -27,6 +27,8 @@
 //                slice; SPC = 2: the same 128 hidden rows for each of the two slices
 #pragma once
 
+#include <type_traits>
+
 #include "ptx_sm100.cuh"
 
 namespace amoe {
@@ -43,6 +45,7 @@ struct MoeParams {
     const float* topk_weights;  // [M, top_k]
     int top_k, M, K, N, E, sorted_num, block_m;
     int stages;                 // ring depth actually used (fits in shared memory)
+    int ksplit;                 // CTAs of a cluster that share one (block, slice): 1 (no cluster), 2, 4 or 8
     float scaling;
     KernelStatus* status;
 #ifdef AMOE_TRACE
@@ -64,11 +67,12 @@ struct MoeParams {
 constexpr int kTileBytes = 128 * 128;  // one 128-row x 128-byte operand tile
 
 struct SmemPlan {
-    uint32_t stage_bytes, hq, xs, swg, swu, sw2, tokrow, topkw, tokscale, amax, bars, misc, total;
+    uint32_t stage_bytes, hq, xs, swg, swu, sw2, tokrow, topkw, tokscale, amax, part, bars, misc, total;
 };
 // Offsets from a 1024-byte aligned base.  bmp = padded block_m, s = ring depth, kc = K/128,
-// spc = slices per CTA.
-__host__ __device__ inline SmemPlan smem_plan(int bmp, int s, int kc, int spc) {
+// spc = slices per CTA, ksplit = CTAs per cluster sharing the K range (their partial sums are exchanged
+// through a [2][bmp][128] fp32 buffer).
+__host__ __device__ inline SmemPlan smem_plan(int bmp, int s, int kc, int spc, int ksplit = 1) {
     SmemPlan p;
     p.stage_bytes = 2 * kTileBytes + bmp * 128;
     uint32_t o = s * p.stage_bytes;
@@ -82,7 +86,8 @@ __host__ __device__ inline SmemPlan smem_plan(int bmp, int s, int kc, int spc) {
     p.topkw = o;     o += bmp * 4;
     p.tokscale = o;  o += spc * bmp * 4;
     p.amax = o;      o += bmp * 16;
-    p.bars = o;      o += (2 * s + 7) * 8;
+    p.part = o;      o += ksplit > 1 ? 2 * bmp * 128 * 4 : 0;
+    p.bars = o;      o += (2 * s + 10) * 8;
     p.misc = o;      o += 16;
     p.total = o;
     return p;
@@ -100,20 +105,41 @@ fused_moe_w8a8_up_down_sm100_kernel(const __grid_constant__ CUtensorMap tm_w,
     static_assert(BMP == 16 || BMP == 32 || BMP == 64 || BMP == 128, "padded block_m");
     static_assert(SPC == 1 || SPC == 2, "slices per CTA");
 
+    // With ksplit > 1 the launch uses clusters of ksplit consecutive CTAs that share one (block, slice):
+    // each takes a contiguous part of the K chunks of the up-projection, the partial sums are exchanged
+    // through distributed shared memory, and each then takes a part of the hidden tiles of the
+    // down-projection.  This is what lets a handful of active experts (small batches) use all SMs.
+    const int ks = p.ksplit;
+    const int crank = ks > 1 ? static_cast<int>(cluster_ctarank()) : 0;
+    const int unit = blockIdx.x / ks;
     const int ngroups = (p.N >> 8) / SPC;
-    const int mblock = blockIdx.x / ngroups;
-    const int slice0 = (blockIdx.x - mblock * ngroups) * SPC;
+    const int mblock = unit / ngroups;
+    const int slice0 = (unit - mblock * ngroups) * SPC;
     const int npad = min(p.num_tokens_post_padded[0], p.sorted_num);
     if (mblock * p.block_m >= npad) return;          // block beyond the padded schedule (reference :678)
     const int expert = p.expert_ids[mblock];
-    if (expert < 0 || expert >= p.E) return;
+    if (expert < 0 || expert >= p.E) return;         // (a whole cluster leaves together: same block)
 
     const int KC = p.K >> 7;                         // 128-deep K chunks of the up-projection
-    const int UPI = SPC * KC;                        // up-projection iterations (slice-major)
-    const int ND = SPC == 1 ? (KC + 1) >> 1 : KC;    // down-projection iterations
+    const int kc_begin = crank * KC / ks, kc_end = (crank + 1) * KC / ks;       // this CTA's K chunks
+    const int nd_all = SPC == 1 ? (KC + 1) >> 1 : KC;
+    const int jt_begin = crank * nd_all / ks;                                   // this CTA's down iterations
+    const int UPI = SPC * (kc_end - kc_begin);       // up-projection iterations (slice-major)
+    const int ND = (crank + 1) * nd_all / ks - jt_begin;                        // down-projection iterations
     const int NIT = UPI + ND;
     const int S = p.stages;
     const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
+    if (threadIdx.x == 0) AMOE_STAMP(6, 0);
+#ifdef AMOE_TRACE
+    if (p.trace && threadIdx.x == 0) {
+        unsigned long long gt;
+        asm volatile("mov.u64 %0, %%globaltimer;" : "=l"(gt));
+        unsigned smid;
+        asm volatile("mov.u32 %0, %%smid;" : "=r"(smid));
+        p.trace[4000 + blockIdx.x * 3] = static_cast<long long>(gt);
+        p.trace[4000 + blockIdx.x * 3 + 2] = smid;
+    }
+#endif
 
     // The operand tiles need 1024-byte alignment (128-byte swizzle atoms).  The dynamic shared memory
     // window is declared with that alignment; should a toolchain ever place it differently, the CTA
@@ -124,7 +150,7 @@ fused_moe_w8a8_up_down_sm100_kernel(const __grid_constant__ CUtensorMap tm_w,
         if (threadIdx.x == 0) atomicCAS(&p.status->code, ST_OK, ST_SMEM_MISALIGNED);
         return;
     }
-    const SmemPlan L = smem_plan(BMP, S, KC, SPC);
+    const SmemPlan L = smem_plan(BMP, S, KC, SPC, ks);
     uint8_t* hq = smem + L.hq;                                        // fp8 intermediate [SPC][BMP][128], swizzled
     float* xs = reinterpret_cast<float*>(smem + L.xs);                // [KC][BMP] token scales
     float* swg = reinterpret_cast<float*>(smem + L.swg);              // [SPC][KC] gate block scales
@@ -140,6 +166,10 @@ fused_moe_w8a8_up_down_sm100_kernel(const __grid_constant__ CUtensorMap tm_w,
     uint64_t* acc_empty = acc_full + 2;
     uint64_t* h_ready = acc_empty + 2;
     uint64_t* xchg = h_ready + 1;                                     // [2] amax exchange inside an epilogue warpgroup
+    uint64_t* peer_ready = xchg + 2;                                  // every CTA of the cluster has published its partial sums
+    uint64_t* peer_done = peer_ready + 1;                             // every CTA of the cluster has finished reading ours
+    uint64_t* xsync = peer_done + 1;                                  // all epilogue warps of this CTA (bounded stand-in for bar.sync)
+    float* part = reinterpret_cast<float*>(smem + L.part);            // [2][BMP][128] this CTA's partial gate / up sums
     uint32_t* tmem_slot = reinterpret_cast<uint32_t*>(smem + L.misc);
     volatile int* abort_flag = reinterpret_cast<volatile int*>(smem + L.misc + 4);
 
@@ -155,6 +185,9 @@ fused_moe_w8a8_up_down_sm100_kernel(const __grid_constant__ CUtensorMap tm_w,
         mbar_init(h_ready, 1);
         mbar_init(&xchg[0], 4);
         mbar_init(&xchg[1], 4);
+        mbar_init(peer_ready, ks);
+        mbar_init(peer_done, ks);
+        mbar_init(xsync, 4 * NEPI_WG);
         *abort_flag = 0;
         fence_mbar_init();
     }
@@ -166,6 +199,9 @@ fused_moe_w8a8_up_down_sm100_kernel(const __grid_constant__ CUtensorMap tm_w,
     __syncthreads();
     tc_fence_after();
     const uint32_t tmem_base = *tmem_slot;
+    if (threadIdx.x == 0) AMOE_STAMP(6, 1);
+    if (ks > 1) cluster_sync_all();      // no CTA may signal a peer's barriers before that peer has initialised them
+    if (threadIdx.x == 0) AMOE_STAMP(6, 2);
 
     if (warp >= W_G0) {
     // ====================================================================== control warpgroup
@@ -215,7 +251,7 @@ fused_moe_w8a8_up_down_sm100_kernel(const __grid_constant__ CUtensorMap tm_w,
                     umma_f8_chunk2(d0, d0 + BMP, a0_up0 + off, a1_up0 + off, x_up0 + off, x_up0 + off, idesc);
                 } else if (SPC == 2) {
                     umma_f8_chunk2(d0, d0 + BMP, a0_dn0 + off, a1_dn0 + off, h0, h1, idesc);
-                } else if (2 * (it - UPI) + 1 < KC) {
+                } else if (2 * (jt_begin + it - UPI) + 1 < KC) {
                     umma_f8_chunk2(d0, d0 + BMP, a0_dn0 + off, a1_dn0 + off, h0, h0, idesc);
                 } else {
                     umma_f8_chunk1(d0, a0_dn0 + off, h0, idesc);
@@ -255,7 +291,7 @@ fused_moe_w8a8_up_down_sm100_kernel(const __grid_constant__ CUtensorMap tm_w,
         bool ok = true;
         int s = 0;                                  // ring slot being filled
         uint32_t ph = 0;
-        int kc = 0, sl = 0;
+        int kc = kc_begin, sl = 0;
         for (int it = 0; it < UPI; ++it) {
             if (tma_thread) AMOE_STAMP(7, it);
             if (!mbar_wait(&empty[s], ph ^ 1, abort_flag, p.status, 30, it)) { ok = false; break; }
@@ -276,14 +312,15 @@ fused_moe_w8a8_up_down_sm100_kernel(const __grid_constant__ CUtensorMap tm_w,
             }
             cp_async_mbar_arrive_noinc(&full[s]);      // arrives when this thread's copies have landed
             if (++s == S) { s = 0; ph ^= 1; }
-            if (++kc == KC) { kc = 0; ++sl; }
+            if (++kc == kc_end) { kc = kc_begin; ++sl; }
         }
         cp_async_wait_all();                        // nothing of this thread may still be in flight at exit
         if (tma_thread && ok) {
             // down phase: this thread keeps feeding w2 tiles; there is no token gather any more, so it
             // also stands in for the 64 gather threads on the slot's barrier
-            for (int jt = 0; jt < ND; ++jt) {
-                const int it = UPI + jt;
+            for (int jl = 0; jl < ND; ++jl) {
+                const int it = UPI + jl;
+                const int jt = jt_begin + jl;
                 AMOE_STAMP(7, it);
                 if (!mbar_wait(&empty[s], ph ^ 1, abort_flag, p.status, 10, it)) break;
                 uint8_t* st = smem + s * L.stage_bytes;
@@ -344,7 +381,9 @@ fused_moe_w8a8_up_down_sm100_kernel(const __grid_constant__ CUtensorMap tm_w,
         for (int j = 0; j < BMP; ++j)
             if (tokrow[j] < p.M) nhi = j + 1;
         const int my_ncols = min(max(nhi - hh * NC, 0), NC);
+        const bool few = nhi <= 2 && NEPI_WG == 1;   // at most two live columns in the whole block (CTA-uniform)
         named_bar_sync(1, EPI_THREADS);
+        if (etid == 0) AMOE_STAMP(6, 3);
 
         float accg[NC], accu[NC];
 #pragma unroll
@@ -360,7 +399,7 @@ fused_moe_w8a8_up_down_sm100_kernel(const __grid_constant__ CUtensorMap tm_w,
         const uint32_t tlane = tmem_base + (static_cast<uint32_t>(q * 32) << 16) + hh * NC;
         bool ok = true;
         int es = 0;                          // ring slot of the chunk being retired (for handing it back)
-        int kc = 0, sl = 0;
+        int kc = kc_begin, sl = 0;
         uint32_t xph = 0;
         // ---- up-projection: promote each K chunk with its scales (reference :915-933)
         for (int it = 0; it < UPI && ok; ++it) {
@@ -399,53 +438,109 @@ fused_moe_w8a8_up_down_sm100_kernel(const __grid_constant__ CUtensorMap tm_w,
             if (lane == 0) mbar_arrive(&acc_empty[b]);
             if (etid == 0) AMOE_STAMP(4, it);
 
-            if (++kc == KC) {
+            if (++kc == kc_end) {
+                if (etid == 0) AMOE_STAMP(10, 0);
+                if (ks > 1) {
+                    // ---- K-split: every CTA of the cluster holds partial sums over its own K chunks.  Publish
+                    // ours in shared memory, tell every peer, wait (bounded) until all peers have published,
+                    // then add up all partial sums straight out of the peers' shared memory.  All CTAs end up
+                    // with the same totals and each re-quantises the intermediate for itself.
+#pragma unroll
+                    for (int j = 0; j < NC; ++j) {
+                        if (j < my_ncols) {
+                            part[(hh * NC + j) * 128 + r] = accg[j];
+                            part[(BMP + hh * NC + j) * 128 + r] = accu[j];
+                        }
+                    }
+                    __syncwarp();
+                    if (lane == 0) mbar_arrive(xsync);
+                    if (!mbar_wait(xsync, 0, abort_flag, p.status, 45, it)) ok = false;
+                    if (etid < ks) mbar_arrive_cluster(mapa_shared(smem_u32(peer_ready), etid));
+                    if (!mbar_wait_cluster(peer_ready, 0, abort_flag, p.status, 43, it)) ok = false;
+                    const uint32_t my_part = smem_u32(part);
+#pragma unroll
+                    for (int j = 0; j < NC; ++j) {
+                        if (j < my_ncols) {
+                            float g = 0.f, u = 0.f;
+                            for (int peer = 0; peer < ks; ++peer) {
+                                const uint32_t base = mapa_shared(my_part, peer);
+                                g += ld_dsmem_f32(base + ((hh * NC + j) * 128 + r) * 4);
+                                u += ld_dsmem_f32(base + ((BMP + hh * NC + j) * 128 + r) * 4);
+                            }
+                            accg[j] = g;
+                            accu[j] = u;
+                        }
+                    }
+                    __syncwarp();
+                    if (lane == 0) mbar_arrive(xsync);       // every thread of this CTA is done reading the peers
+                    if (!mbar_wait(xsync, 1, abort_flag, p.status, 46, it)) ok = false;
+                    if (etid < ks) mbar_arrive_cluster(mapa_shared(smem_u32(peer_done), etid));
+                }
+                if (etid == 0) AMOE_STAMP(10, 1);
                 // ---- end of a slice: SwiGLU, per-token amax over the slice's 128 columns, fp8 re-quantisation
                 //      (reference :936-1005; h stays in registers, only the fp8 tile goes to shared memory)
+                // Blocks of one or two tokens are the rule at small batch: then only the first two columns are
+                // worked on and the other rows of the intermediate tile are written as zeros.
+                auto swiglu_quant = [&](auto live_cols) {
+                    constexpr int NJ = decltype(live_cols)::value;
 #pragma unroll
-                for (int j = 0; j < NC; ++j) {
-                    const float g = bf16_round(accg[j]);
-                    const float u = bf16_round(accu[j]);
-                    const float h = bf16_round(__fdividef(g, 1.0f + __expf(-g)) * u);
-                    accg[j] = h;
-                    const uint32_t a = __reduce_max_sync(0xFFFFFFFFu, __float_as_uint(fabsf(h)));
-                    if (lane == 0) amax_part[(hh * NC + j) * 4 + q] = a;
-                }
-                // exchange of the four warps' maxima through a (bounded) mbarrier rather than bar.sync, so that
-                // a warp that gave up on a wait can never leave the others parked at a hardware barrier
-                __syncwarp();
-                if (lane == 0) mbar_arrive(&xchg[hh]);
-                if (!mbar_wait(&xchg[hh], xph, abort_flag, p.status, 42, it)) ok = false;
-                xph ^= 1;
-                uint8_t* hq_sl = hq + sl * BMP * 128;
-#pragma unroll
-                for (int j = 0; j < NC; ++j) {
-                    const int col = hh * NC + j;
-                    const uint4 pm = *reinterpret_cast<const uint4*>(amax_part + col * 4);
-                    const float amax = __uint_as_float(max(max(pm.x, pm.y), max(pm.z, pm.w)));
-                    const float s_h = fmaxf(amax, 1e-10f) * (1.0f / 448.0f);
-                    const float qv = fminf(fmaxf(__fdividef(accg[j], s_h), -448.0f), 448.0f);
-                    const uint8_t qb = static_cast<uint8_t>(__nv_cvt_float_to_fp8(qv, __NV_SATFINITE, __NV_E4M3));
-                    hq_sl[col * 128 + ((((r >> 4) ^ (col & 7)) << 4) | (r & 15))] = qb;
-                    const float fac = s_h * topkw[col] * p.scaling;
-                    if constexpr (kFactorsInRegs) {
-                        facj[j] = fac;
-                        rowj[j] = tokrow[col];
-                    } else {
-                        if (r == 0) tokscale[sl * BMP + col] = fac;
+                    for (int j = 0; j < NJ; ++j) {
+                        const float g = bf16_round(accg[j]);
+                        const float u = bf16_round(accu[j]);
+                        const float h = bf16_round(__fdividef(g, 1.0f + __expf(-g)) * u);
+                        accg[j] = h;
+                        const uint32_t a = __reduce_max_sync(0xFFFFFFFFu, __float_as_uint(fabsf(h)));
+                        if (lane == 0) amax_part[(hh * NC + j) * 4 + q] = a;
                     }
-                    accg[j] = 0.f;
-                    accu[j] = 0.f;
-                }
+                    // exchange of the four warps' maxima through a (bounded) mbarrier rather than bar.sync, so
+                    // that a warp that gave up on a wait can never leave the others parked at a hardware barrier
+                    __syncwarp();
+                    if (lane == 0) mbar_arrive(&xchg[hh]);
+                    if (!mbar_wait(&xchg[hh], xph, abort_flag, p.status, 42, it)) ok = false;
+                    xph ^= 1;
+                    uint8_t* hq_sl = hq + sl * BMP * 128;
+#pragma unroll
+                    for (int j = 0; j < NC; ++j) {
+                        const int col = hh * NC + j;
+                        const uint32_t hoff = col * 128 + ((((r >> 4) ^ (col & 7)) << 4) | (r & 15));
+                        if (j < NJ) {
+                            const uint4 pm = *reinterpret_cast<const uint4*>(amax_part + col * 4);
+                            const float amax = __uint_as_float(max(max(pm.x, pm.y), max(pm.z, pm.w)));
+                            const float s_h = fmaxf(amax, 1e-10f) * (1.0f / 448.0f);
+                            const float qv = fminf(fmaxf(__fdividef(accg[j], s_h), -448.0f), 448.0f);
+                            hq_sl[hoff] = static_cast<uint8_t>(__nv_cvt_float_to_fp8(qv, __NV_SATFINITE, __NV_E4M3));
+                            const float fac = s_h * topkw[col] * p.scaling;
+                            if constexpr (kFactorsInRegs) {
+                                facj[j] = fac;
+                                rowj[j] = tokrow[col];
+                            } else {
+                                if (r == 0) tokscale[sl * BMP + col] = fac;
+                            }
+                        } else {
+                            hq_sl[hoff] = 0;
+                            if constexpr (kFactorsInRegs) {
+                                facj[j] = 0.f;
+                                rowj[j] = p.M;
+                            } else {
+                                if (r == 0) tokscale[sl * BMP + col] = 0.f;
+                            }
+                        }
+                        accg[j] = 0.f;
+                        accu[j] = 0.f;
+                    }
+                };
+                if (few) swiglu_quant(std::integral_constant<int, (NC < 2 ? NC : 2)>{});
+                else swiglu_quant(std::integral_constant<int, NC>{});
                 fence_proxy_async_smem();
                 // (amax_part is rewritten at the end of the next slice; the acc_empty hand-shake keeps the four
                 //  warps within two chunks of each other, so every read above has long completed by then)
-                kc = 0;
+                kc = kc_begin;
                 ++sl;
             }
         }
         named_bar_sync(1, EPI_THREADS);
         if (etid == 0) mbar_arrive(h_ready);
+        if (etid == 0) AMOE_STAMP(10, 2);
 
         // ---- down-projection epilogue: scale, pair adjacent hidden columns, bf16x2 reduce into out
         //      (reference :1052-1094 goes through stmatrix + per-row bulk reduce).
@@ -453,8 +548,9 @@ fused_moe_w8a8_up_down_sm100_kernel(const __grid_constant__ CUtensorMap tm_w,
         // reduction is issued: tcgen05.fence / mbarrier.arrive after a global reduction would wait for
         // L2 to acknowledge it, which would put an L2 round trip into every iteration.
         const bool odd = lane & 1;
-        for (int jt = 0; jt < ND && ok; ++jt) {
-            const int it = UPI + jt;
+        for (int jl = 0; jl < ND && ok; ++jl) {
+            const int it = UPI + jl;
+            const int jt = jt_begin + jl;            // hidden-tile pair (SPC = 1) / hidden tile (SPC = 2) of the whole layer
             const int b = it & 1;
             const uint32_t aph = (it >> 1) & 1;
             if (!mbar_wait(&acc_full[b], aph, abort_flag, p.status, 41, it)) { ok = false; break; }
@@ -493,6 +589,7 @@ fused_moe_w8a8_up_down_sm100_kernel(const __grid_constant__ CUtensorMap tm_w,
                             if (c0 < my_ncols) {
 #pragma unroll
                                 for (int j = c0; j < c0 + 16; j += 2) {
+                                    if (j >= 2 && few) break;      // one or two live columns: the first pair is all there is
                                     float f0, f1;
                                     int r0, r1;
                                     if constexpr (kFactorsInRegs) {
@@ -524,6 +621,7 @@ fused_moe_w8a8_up_down_sm100_kernel(const __grid_constant__ CUtensorMap tm_w,
                     if (c0 < my_ncols) {
 #pragma unroll
                         for (int j = c0; j < c0 + 16; j += 2) {
+                            if (j >= 2 && few) break;
                             const float2 fa = *reinterpret_cast<const float2*>(tokscale + hh * NC + j);
                             const float2 fb = *reinterpret_cast<const float2*>(tokscale + BMP + hh * NC + j);
                             const int2 rr = *reinterpret_cast<const int2*>(tokrow + hh * NC + j);
@@ -542,6 +640,9 @@ fused_moe_w8a8_up_down_sm100_kernel(const __grid_constant__ CUtensorMap tm_w,
             }
             if (etid == 0) AMOE_STAMP(5, it);
         }
+        if (etid == 0) AMOE_STAMP(10, 3);
+        // our partial sums must stay readable until every peer of the cluster has read them
+        if (ks > 1 && etid == 0) mbar_wait_cluster(peer_done, 0, abort_flag, p.status, 44, NIT);
     }
 
     tc_fence_before();
@@ -550,6 +651,13 @@ fused_moe_w8a8_up_down_sm100_kernel(const __grid_constant__ CUtensorMap tm_w,
         tc_fence_after();
         tmem_dealloc(tmem_base, TMEM_COLS);
     }
+#ifdef AMOE_TRACE
+    if (p.trace && threadIdx.x == 0) {
+        unsigned long long gt;
+        asm volatile("mov.u64 %0, %%globaltimer;" : "=l"(gt));
+        p.trace[4000 + blockIdx.x * 3 + 1] = static_cast<long long>(gt);
+    }
+#endif
 }
 
 }  // namespace amoe

@@ -10,6 +10,7 @@
 
 #include <cstdarg>
 #include <cstdio>
+#include <cstdlib>
 #include <cstring>
 #include <map>
 #include <mutex>
@@ -132,13 +133,13 @@ int padded_block_m(int block_m) { return block_m <= 16 ? 16 : block_m <= 32 ? 32
 bool token_major(int block_m) { return block_m > 64; }
 
 // Ring depth = the `stages` knob, lowered until the plan fits in shared memory.
-int plan(int K, int block_m, int stages, int spc, int* depth, int* bmp, int* smem_bytes) {
+int plan(int K, int block_m, int stages, int spc, int ksplit, int* depth, int* bmp, int* smem_bytes) {
     const int kc = K / 128;
     const int b = padded_block_m(block_m);
     int s = stages;
     for (; s >= 1; --s) {
         const int need = static_cast<int>(token_major(block_m) ? amoe::smem_plan_tm(s, kc, spc).total
-                                                               : amoe::smem_plan(b, s, kc, spc).total);
+                                                               : amoe::smem_plan(b, s, kc, spc, ksplit).total);
         if (need <= kMaxDynSmem) {
             *depth = s;
             *bmp = b;
@@ -161,6 +162,22 @@ int launch_variant(const CUtensorMap& mw, const CUtensorMap& mw2, const amoe::Mo
         configured_smem[dev] = kMaxDynSmem;
     }
     constexpr int threads = 128 * (BMP >= 64 ? 2 : 1) + 128;
+    if (p.ksplit > 1) {
+        cudaLaunchConfig_t cfg = {};
+        cfg.gridDim = dim3(static_cast<unsigned>(grid));
+        cfg.blockDim = dim3(threads);
+        cfg.dynamicSmemBytes = static_cast<size_t>(smem_bytes);
+        cfg.stream = stream;
+        cudaLaunchAttribute attr;
+        attr.id = cudaLaunchAttributeClusterDimension;
+        attr.val.clusterDim.x = static_cast<unsigned>(p.ksplit);
+        attr.val.clusterDim.y = 1;
+        attr.val.clusterDim.z = 1;
+        cfg.attrs = &attr;
+        cfg.numAttrs = 1;
+        CUDA_TRY(cudaLaunchKernelEx(&cfg, kern, mw, mw2, p));
+        return ALPHA_MOE_OK;
+    }
     kern<<<grid, threads, smem_bytes, stream>>>(mw, mw2, p);
     CUDA_TRY(cudaGetLastError());
     return ALPHA_MOE_OK;
@@ -213,8 +230,26 @@ int alpha_moe_b200_fused_moe_w8a8_up_down(const void* x, const float* x_scale, c
     // block_n = 64 asks for the wide variant: one CTA owns two 128-column slices of the intermediate
     // dimension (one reduction per token and expert instead of two); it needs an even slice count.
     const int spc = (block_n == 64 && (N / 256) % 2 == 0) ? 2 : 1;
+    // Live blocks never exceed the number of assignments, so no more CTAs than that are launched.
+    long long nblocks = (static_cast<long long>(sorted_num) + block_m - 1) / block_m;
+    if (nblocks > static_cast<long long>(M) * top_k) nblocks = static_cast<long long>(M) * top_k;
+    // Small batches activate few experts: split each (block, slice) over a cluster of 2 or 4 CTAs along K
+    // while the CTAs still fit one per SM (narrow tile, one slice per CTA only; 8 is accepted through
+    // ALPHA_MOE_KSPLIT but measured no faster than 4).
+    int ksplit = 1;
+    if (block_m <= 32 && spc == 1) {
+        int sms = 0, dev_now = 0;
+        CUDA_TRY(cudaGetDevice(&dev_now));
+        CUDA_TRY(cudaDeviceGetAttribute(&sms, cudaDevAttrMultiProcessorCount, dev_now));
+        const long long live_max = nblocks * (N / 256);
+        while (ksplit < 4 && live_max * ksplit * 2 <= sms && ksplit * 2 <= K / 128) ksplit *= 2;
+        if (const char* env = getenv("ALPHA_MOE_KSPLIT")) {
+            const int v = atoi(env);
+            if ((v == 1 || v == 2 || v == 4 || v == 8) && v <= K / 128) ksplit = v;
+        }
+    }
     int depth, bmp, smem_bytes;
-    if (int rc = plan(K, block_m, stages, spc, &depth, &bmp, &smem_bytes)) return rc;
+    if (int rc = plan(K, block_m, stages, spc, ksplit, &depth, &bmp, &smem_bytes)) return rc;
 
     int dev = 0;
     CUDA_TRY(cudaGetDevice(&dev));
@@ -242,6 +277,7 @@ int alpha_moe_b200_fused_moe_w8a8_up_down(const void* x, const float* x_scale, c
     p.sorted_num = sorted_num;
     p.block_m = block_m;
     p.stages = depth;
+    p.ksplit = ksplit;
     p.scaling = scaling_factor;
     p.status = status;
 #ifdef AMOE_TRACE
@@ -249,8 +285,7 @@ int alpha_moe_b200_fused_moe_w8a8_up_down(const void* x, const float* x_scale, c
     p.trace_block = g_trace_block;
 #endif
 
-    const long long nblocks = (static_cast<long long>(sorted_num) + block_m - 1) / block_m;
-    const long long grid = nblocks * (N / 256 / spc);
+    const long long grid = nblocks * (N / 256 / spc) * ksplit;
     if (grid > 0x7FFFFFFFLL) return fail(ALPHA_MOE_E_ARG, "grid too large");
     cudaStream_t st = static_cast<cudaStream_t>(stream);
     const int g = static_cast<int>(grid);
@@ -298,7 +333,7 @@ int alpha_moe_b200_plan(int K, int block_m, int block_n, int stages, int32_t* ou
     if (stages < 1 || stages > 5) return fail(ALPHA_MOE_E_ARG, "stages must be in 1..5, got %d", stages);
     const int spc = block_n == 64 ? 2 : 1;
     int depth, bmp, smem_bytes;
-    if (int rc = plan(K, block_m, stages, spc, &depth, &bmp, &smem_bytes)) return rc;
+    if (int rc = plan(K, block_m, stages, spc, 1, &depth, &bmp, &smem_bytes)) return rc;
     out4[0] = depth;
     out4[1] = bmp;
     out4[2] = smem_bytes;

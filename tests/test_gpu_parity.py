@@ -158,3 +158,21 @@ def test_torch_operator_path_and_errors():
         torch.ops.alpha_moe.fused_moe_w8a8_up_down(
             d["x"], d["x_scale"], d["w"], d["w_scale"], d["w2"], d["w2_scale"], sid, eid, npp,
             d["topk_weights"], out.float(), 2, 16, 32, 8, 3, 1.0)
+
+
+@pytest.mark.parametrize("ks", [1, 2, 4, 8])
+def test_k_split_over_a_cluster_small_batches(ks, monkeypatch):
+    """Small batches: each (block, slice) is shared by a cluster of ks CTAs that split K and exchange partial
+    sums through distributed shared memory.  ALPHA_MOE_KSPLIT overrides the automatic choice."""
+    monkeypatch.setenv("ALPHA_MOE_KSPLIT", str(ks))
+    w = test_deepseek_shard_shape_small_expert_count.weights
+    for m, top_k in ((1, 5), (3, 5), (7, 3)):
+        case = orc.make_case(16, 7168, 256, m, top_k, seed=50 + m, shared=True, scaling=2.5, weights=w)
+        dcase = to_device(case)
+        for bm, st in ((16, 2), (8, 5), (32, 3)):
+            if m < bm and bm != 16:
+                continue
+            check_close(run_capi(case, bm, 32, 8, st, dcase=dcase), orc.run_oracle(case, bm), tag=f"ks={ks} M={m} bm={bm}")
+    # K with a chunk count that does not divide by ks, and an odd number of hidden tiles
+    case = orc.make_case(8, 1152, 128, 2, 2, seed=9)
+    check_close(run_capi(case, 16, 32, 8, 3), orc.run_oracle(case, 16), tag=f"ks={ks} K=1152")
