@@ -1,0 +1,64 @@
+"""Tensor-parallel run on real GPUs: two ranks (one process per GPU, NCCL) each run the fused operator on
+their I/2 shard and all-reduce the partial bf16 outputs; rank 0 compares with the unsharded single-GPU
+result (rel-L2 <= 1e-2).  Skipped with fewer than two GPUs."""
+import os
+import socket
+import sys
+
+import pytest
+import torch
+
+pytestmark = pytest.mark.gpu
+ROOT = os.path.dirname(os.path.dirname(os.path.abspath(__file__)))
+
+
+def _free_port():
+    with socket.socket() as s:
+        s.bind(("127.0.0.1", 0))
+        return s.getsockname()[1]
+
+
+def _worker(rank, world, port, result_path):
+    sys.path.insert(0, ROOT)
+    os.environ["MASTER_ADDR"] = "127.0.0.1"
+    os.environ["MASTER_PORT"] = str(port)
+    os.environ["NCCL_NVLS_ENABLE"] = "0"
+    import torch.distributed as dist
+    torch.cuda.set_device(rank)
+    dev = torch.device("cuda", rank)
+    dist.init_process_group("nccl", rank=rank, world_size=world, device_id=dev)
+    import alpha_moe  # noqa: F401
+    from alpha_moe_b200.tp import shard_weights, tp_layer
+    from oracle import moe_oracle as orc
+    case = orc.make_case(16, 1024, 512, 70, 5, seed=31, shared=True, scaling=2.5)
+    sid, eid, npp = case.schedule(16)
+    full = [t.to(dev) for t in (case.w, case.w_scale, case.w2, case.w2_scale)]
+    shard = shard_weights(*full, rank, world)
+    x, xs, wts = case.x.to(dev), case.x_scale.to(dev), case.topk_weights.to(dev)
+    sid, eid, npp = sid.to(dev), eid.to(dev), npp.to(dev)
+
+    def run(weights):
+        def compute(out):
+            torch.ops.alpha_moe.fused_moe_w8a8_up_down(x, xs, *weights, sid, eid, npp, wts, out, case.top_k,
+                                                       16, 64, 4, 3, 2.5)
+        return compute
+    out = torch.full((70, 1024), 5.0, dtype=torch.bfloat16, device=dev)
+    tp_layer(run(shard), out)
+    torch.cuda.synchronize()
+    if rank == 0:
+        ref = torch.zeros(70, 1024, dtype=torch.bfloat16, device=dev)
+        run(full)(ref)
+        torch.cuda.synchronize()
+        torch.save({"rel": orc.rel_l2(out.cpu(), ref.cpu()),
+                    "rel_oracle": orc.rel_l2(out.cpu(), orc.run_oracle(case, 16))}, result_path)
+    dist.barrier()
+    dist.destroy_process_group()
+
+
+@pytest.mark.skipif(torch.cuda.device_count() < 2, reason="needs two GPUs")
+def test_tp2_nccl_allreduce_equals_single_gpu(tmp_path):
+    import torch.multiprocessing as mp
+    result = str(tmp_path / "r.pt")
+    mp.spawn(_worker, args=(2, _free_port(), result), nprocs=2, join=True)
+    r = torch.load(result)
+    assert r["rel"] <= 1e-2 and r["rel_oracle"] <= 2e-2
