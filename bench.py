@@ -32,7 +32,7 @@ FP8_MAX_BYTE = 0x78   # random bytes below this are finite e4m3 values
 
 # dram__bytes_read.sum + dram__bytes_write.sum of one launch of the fused kernel, from the ncu
 # capture summarised under profiles/ (bytes per launch, keyed by M); None = not captured.
-NCU_DRAM_TRAFFIC = {64: 1.2346e9 + 5.0e6, 4096: 2.0389e9 + 347.5e6}
+NCU_DRAM_TRAFFIC = {1: 49.66e6 + 0.04e6, 64: 1.2302e9 + 5.9e6, 4096: 1.8367e9 + 151.4e6}
 
 
 def best_knobs(m: int):
@@ -271,7 +271,7 @@ def main():
     ap.add_argument("--m", type=int, default=4096, help="tokens per step of the headline number")
     ap.add_argument("--no-sweep", action="store_true", help="skip the M sweep")
     ap.add_argument("--no-cpu", action="store_true", help="skip the CPU baseline leg")
-    ap.add_argument("--cpu-experts", type=int, default=128, help="experts in the CPU sample")
+    ap.add_argument("--cpu-experts", type=int, default=257, help="experts in the CPU sample (257 = the whole workload)")
     args = ap.parse_args()
     args.warmup = max(args.warmup, 3) if args.impl == "ours" else max(args.warmup, 1)
 

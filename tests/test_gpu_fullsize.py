@@ -40,14 +40,14 @@ def _inputs(m, dev, seed):
     return x, xs, ids, wts
 
 
-def _run(wd, x, xs, ids, wts, bm, scaling, stages=3):
+def _run(wd, x, xs, ids, wts, bm, scaling, stages=3, bn=64):
     import alpha_moe  # noqa: F401
+    from alpha_moe_b200.prologue import moe_align_block_size
     dev = wd[0].device
-    sid, eid, npp = orc.moe_align_block_size(ids, bm, E)
+    sid, eid, npp = moe_align_block_size(ids.to(dev), bm, E)          # this library's schedule kernel
     out = torch.zeros(x.shape[0], K, dtype=torch.bfloat16, device=dev)
-    torch.ops.alpha_moe.fused_moe_w8a8_up_down(x.to(dev), xs.to(dev), wd[0], wd[1], wd[2], wd[3], sid.to(dev),
-                                               eid.to(dev), npp.to(dev), wts.to(dev), out, TOP_K, bm, 32, 8, stages,
-                                               scaling)
+    torch.ops.alpha_moe.fused_moe_w8a8_up_down(x.to(dev), xs.to(dev), wd[0], wd[1], wd[2], wd[3], sid, eid, npp,
+                                               wts.to(dev), out, TOP_K, bm, bn, 8 if bn == 32 else 4, stages, scaling)
     torch.cuda.synchronize()
     from alpha_moe_b200 import capi
     assert capi.read_status(reset=True)[0] == 0
@@ -77,6 +77,31 @@ def test_sampled_tokens_match_the_oracle(weights, m, bm):
     assert r <= 2e-2, f"M={m}: rel-L2 {r}"
     d = (got[sample].float() - ref.float()).abs()
     assert float((d - (0.25 * ref.float().pow(2).mean().sqrt() + 0.1 * ref.float().abs())).max()) <= 0
+
+
+def test_skewed_prefill_zipf_routing_at_full_size(weights):
+    """M=8192 tokens, routed experts drawn from Zipf(1.2) with seed 1: several experts get nothing, a few get more
+    than 10 % of the tokens (dozens of blocks), so the schedule mixes empty experts, ragged last blocks and heavy
+    load imbalance.  Sampled tokens against the oracle, for the weight-major and the token-major kernel."""
+    m = 8192
+    g = torch.Generator().manual_seed(1)
+    x, xs = orc.quant_token_groups(torch.randn(m, K, generator=g).to(torch.bfloat16))
+    ids, wts = orc.route_zipf(m, E - 1, TOP_K - 1, 1.2, g, shared_expert=E - 1)
+    counts = torch.bincount(ids.reshape(-1).long(), minlength=E)
+    assert (counts[:-1] == 0).any() and counts[:-1].max() > 0.1 * m
+    sample = torch.randperm(m, generator=g)[:6]
+    experts = torch.unique(ids[sample]).tolist()
+    remap = {e: i for i, e in enumerate(experts)}
+    sub_ids = torch.tensor([[remap[int(e)] for e in row] for row in ids[sample]], dtype=torch.int32)
+    idx = torch.tensor(experts)
+    wc = [t[idx.to(t.device)].cpu() for t in weights]
+    ssid, seid, snpp = orc.moe_align_block_size(sub_ids, 16, len(experts))
+    ref = orc.fused_moe_w8a8_up_down_oracle(x[sample], xs[sample], wc[0], wc[1], wc[2], wc[3], ssid, seid, snpp,
+                                            wts[sample].contiguous(), TOP_K, 16, 2.5)
+    for bm in (64, 128):
+        got = _run(weights, x, xs, ids, wts, bm, 2.5)
+        assert orc.rel_l2(got[sample], ref) <= 2e-2, f"bm={bm}"
+        assert torch.isfinite(got.float()).all()
 
 
 def test_block_m_invariance_and_linearity_at_full_size(weights):
