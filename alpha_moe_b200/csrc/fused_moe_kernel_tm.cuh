@@ -31,6 +31,7 @@ namespace amoe {
 constexpr int kTmRows = 128;   // token rows of a block (TMEM lanes)
 constexpr int kStgPitch = 144;                     // staging row pitch: 128 B + 16 B so that rows spread over the banks
 constexpr int kStgWarpBytes = 32 * kStgPitch;      // one warp's staging tile
+constexpr uint32_t kStgAliased = 0xFFFFFFFFu;      // SmemPlanTm::stage_out when the staging tiles alias the ring
 
 struct SmemPlanTm {
     uint32_t stage_bytes, hq, stage_out, swg, swu, sw2, amaxx, bars, misc, total;
@@ -40,7 +41,9 @@ __host__ __device__ inline SmemPlanTm smem_plan_tm(int s, int kc, int spc) {
     p.stage_bytes = 2 * kTileBytes + kTmRows * 128;
     uint32_t o = s * p.stage_bytes;
     p.hq = o;     o += spc * kTmRows * 128;
-    p.stage_out = o;  o += 8 * kStgWarpBytes;   // per epilogue warp: 32 rows x 128 B (+16 B pitch padding)
+    // per epilogue warp a staging tile of 32 rows x 128 B (+16 B pitch padding) for the down phase; with three
+    // or more ring slots these live in the slots' token-row tiles, which that phase does not use
+    if (s >= 3) { p.stage_out = kStgAliased; } else { p.stage_out = o;  o += 8 * kStgWarpBytes; }
     p.swg = o;    o += spc * kc * 4;
     p.swu = o;    o += spc * kc * 4;
     p.sw2 = o;    o += spc * kc * 4;
@@ -59,12 +62,19 @@ __device__ __forceinline__ void red_add_v4_bf16x2_raw_if(__nv_bfloat16* addr, co
         ::"l"(addr), "r"(w.x), "r"(w.y), "r"(w.z), "r"(w.w), "r"(static_cast<uint32_t>(pred)));
 }
 
+constexpr int kTmThreads = 512;     // 2 epilogue warpgroups + control warpgroup + gather warpgroup
+constexpr int kTmGatherWarps = 5;   // one warp of the control warpgroup + the gather warpgroup
+
 template <int SPC>
-__global__ void __launch_bounds__(384, 1)
+__global__ void __launch_bounds__(kTmThreads, 1)
 fused_moe_w8a8_up_down_sm100_tokmajor_kernel(const __grid_constant__ CUtensorMap tm_w,
                                              const __grid_constant__ CUtensorMap tm_w2, const MoeParams p) {
     constexpr int EPI_THREADS = 256;
-    constexpr int W_G0 = 8, W_MMA0 = 10;         // control warpgroup: gather(+TMA), gather, UMMA, UMMA
+    // control warpgroup: weight TMA, gather, UMMA (even chunks), UMMA (odd chunks); then four more gather warps.
+    // One warp issues a 16-byte cp.async of 32 lanes only about every 100 cycles, whatever the addresses, and a
+    // 128-row x 128-byte token tile takes 32 of them: five warps bring a tile in about as long as its UMMAs run.
+    constexpr int W_TMA = 8, W_G0 = 9, W_MMA0 = 10, W_G1 = 12;
+    constexpr int GATHER_THREADS = kTmGatherWarps * 32;
     constexpr uint32_t TMEM_COLS = 512;
     static_assert(SPC == 1 || SPC == 2, "slices per CTA");
 
@@ -106,10 +116,11 @@ fused_moe_w8a8_up_down_sm100_tokmajor_kernel(const __grid_constant__ CUtensorMap
     uint64_t* xchg = h_ready + 1;
     uint32_t* tmem_slot = reinterpret_cast<uint32_t*>(smem + L.misc);
     volatile int* abort_flag = reinterpret_cast<volatile int*>(smem + L.misc + 4);
+    volatile int* issue_turn = reinterpret_cast<volatile int*>(smem + L.misc + 8);   // iterations whose operands have been waited for
 
-    if (threadIdx.x == W_G0 * 32) {
+    if (threadIdx.x == W_TMA * 32) {
         for (int i = 0; i < S; ++i) {
-            mbar_init(&full[i], 1 + 64);
+            mbar_init(&full[i], 1 + GATHER_THREADS);
             mbar_init(&empty[i], 1);
         }
         for (int i = 0; i < 2; ++i) {
@@ -119,6 +130,7 @@ fused_moe_w8a8_up_down_sm100_tokmajor_kernel(const __grid_constant__ CUtensorMap
         mbar_init(h_ready, 1);
         mbar_init(&xchg[0], 8);
         *abort_flag = 0;
+        *issue_turn = 0;
         fence_mbar_init();
     }
     if (warp == W_MMA0) {
@@ -130,10 +142,10 @@ fused_moe_w8a8_up_down_sm100_tokmajor_kernel(const __grid_constant__ CUtensorMap
     tc_fence_after();
     const uint32_t tmem_base = *tmem_slot;
 
-    if (warp >= W_G0) {
-    // ====================================================================== control warpgroup
-    setmaxnreg_dec<64>();
-    if (warp >= W_MMA0) {
+    if (warp >= W_TMA) {
+    // ====================================================================== control + gather warpgroups
+    setmaxnreg_dec<40>();
+    if (warp == W_MMA0 || warp == W_MMA0 + 1) {
         // ------------------------------------------------------------------ UMMA issuers (even / odd chunks)
         if (lane == 0) {
             const int pw = warp - W_MMA0;
@@ -162,7 +174,31 @@ fused_moe_w8a8_up_down_sm100_tokmajor_kernel(const __grid_constant__ CUtensorMap
                 }
                 if (!mbar_wait(&acc_empty[b], aph ^ 1, abort_flag, p.status, 21, it)) break;
                 AMOE_STAMP(9, it);
+                // The two issuers take their turns in iteration order.  A parity wait is only meaningful while
+                // the waiter is at most one phase ahead of the barrier: waiting for fill n of a slot presumes
+                // that fill n-1 has completed.  Fill n-1 belongs to iteration it-S, which with an odd ring depth
+                // is the other issuer's; in the down phase the two warpgroups of the epilogue release the
+                // accumulator buffers independently, so without the turn one issuer could get that far ahead.
+                {
+                    const long long t0 = clock64();
+                    bool turn_ok = true;
+                    while (*issue_turn < it) {
+                        if (*abort_flag) { turn_ok = false; break; }
+                        if (clock64() - t0 > kWaitLimitCycles) {
+                            *abort_flag = 1;
+                            if (atomicCAS(&p.status->code, ST_OK, ST_WAIT_TIMEOUT) == ST_OK) {
+                                p.status->block = blockIdx.x;
+                                p.status->where = 23;
+                                p.status->iter = it;
+                            }
+                            turn_ok = false;
+                            break;
+                        }
+                    }
+                    if (!turn_ok) break;
+                }
                 if (!mbar_wait(&full[s], ph, abort_flag, p.status, 22, it)) break;
+                *issue_turn = it + 1;
                 fence_proxy_async_smem();      // token rows were written by cp.async, the UMMA reads them through the async proxy
                 tc_fence_after();
                 AMOE_STAMP(1, it);
@@ -181,72 +217,84 @@ fused_moe_w8a8_up_down_sm100_tokmajor_kernel(const __grid_constant__ CUtensorMap
                 while (s >= S) { s -= S; ph ^= 1; }
             }
         }
-    } else {
-        // ------------------------------------------------------------------ token-row gather (2 warps) + weight TMA
-        constexpr int PIECES = kTmRows / 8;
-        const int gtid = threadIdx.x - W_G0 * 32;
-        const bool tma_thread = gtid == 0;
-        const int row0 = gtid >> 3, ch = gtid & 7;
-        uint32_t src16[PIECES];
-#pragma unroll
-        for (int i = 0; i < PIECES; ++i) {
-            const int row = row0 + 8 * i;
-            const int idx = mblock * p.block_m + row;
-            src16[i] = 0xFFFFFFFFu;
-            if (row < p.block_m && idx < p.sorted_num) {
-                const int pid = p.sorted_token_ids[idx];
-                if (pid >= 0 && pid < p.M * p.top_k)
-                    src16[i] = static_cast<uint32_t>((static_cast<size_t>(pid / p.top_k) * p.K) >> 4);
-            }
-        }
-        if (tma_thread) {
+    } else if (warp == W_TMA) {
+        // ------------------------------------------------------------------ weight TMA (one thread)
+        if (lane == 0) {
             prefetch_tmap(&tm_w);
             prefetch_tmap(&tm_w2);
-        }
-        const uint32_t dst0 = row0 * 128 + ((ch ^ (row0 & 7)) << 4);
-        bool ok = true;
-        int s = 0;
-        uint32_t ph = 0;
-        int kc = 0, sl = 0;
-        for (int it = 0; it < UPI; ++it) {
-            if (tma_thread) AMOE_STAMP(7, it);
-            if (!mbar_wait(&empty[s], ph ^ 1, abort_flag, p.status, 30, it)) { ok = false; break; }
-            uint8_t* st = smem + s * L.stage_bytes;
-            if (tma_thread) {
+            int s = 0;
+            uint32_t ph = 0;
+            int kc = 0, sl = 0;
+            for (int it = 0; it < NIT; ++it) {
+                AMOE_STAMP(7, it);
+                if (!mbar_wait(&empty[s], ph ^ 1, abort_flag, p.status, 30, it)) break;
+                uint8_t* st = smem + s * L.stage_bytes;
                 AMOE_STAMP(0, it);
                 mbar_arrive_expect_tx(&full[s], 2 * kTileBytes);
-                tma_load_3d(st, &tm_w, &full[s], kc * 128, (slice0 + sl) * 256, expert);
-            }
-            const uint32_t base = smem_u32(st + 2 * kTileBytes) + dst0;
-            const uint8_t* col = p.x + kc * 128 + ch * 16;
-#pragma unroll
-            for (int i = 0; i < PIECES; ++i) {
-                const bool v = src16[i] != 0xFFFFFFFFu;
-                const uint8_t* src = v ? col + (static_cast<size_t>(src16[i]) << 4) : p.x;
-                cp_async_16(base + i * 1024, src, v ? 16u : 0u);
-            }
-            cp_async_mbar_arrive_noinc(&full[s]);      // arrives when this thread's copies have landed
-            if (++s == S) { s = 0; ph ^= 1; }
-            if (++kc == KC) { kc = 0; ++sl; }
-        }
-        cp_async_wait_all();                        // nothing of this thread may still be in flight at exit
-        if (tma_thread && ok) {
-            for (int jt = 0; jt < ND; ++jt) {
-                const int it = UPI + jt;
-                if (!mbar_wait(&empty[s], ph ^ 1, abort_flag, p.status, 10, it)) break;
-                uint8_t* st = smem + s * L.stage_bytes;
-                mbar_arrive_expect_tx(&full[s], 2 * kTileBytes);
-                if (SPC == 1) {
-                    tma_load_3d(st, &tm_w2, &full[s], slice0 * 128, (2 * jt) * 128, expert);
-                    tma_load_3d(st + kTileBytes, &tm_w2, &full[s], slice0 * 128, (2 * jt + 1) * 128, expert);
+                if (it < UPI) {
+                    tma_load_3d(st, &tm_w, &full[s], kc * 128, (slice0 + sl) * 256, expert);
+                    if (++kc == KC) { kc = 0; ++sl; }
                 } else {
-                    tma_load_3d(st, &tm_w2, &full[s], slice0 * 128, jt * 128, expert);
-                    tma_load_3d(st + kTileBytes, &tm_w2, &full[s], (slice0 + 1) * 128, jt * 128, expert);
+                    // down phase: no token rows any more, so this thread also stands in for the gather threads
+                    const int jt = it - UPI;
+                    if (SPC == 1) {
+                        tma_load_3d(st, &tm_w2, &full[s], slice0 * 128, (2 * jt) * 128, expert);
+                        tma_load_3d(st + kTileBytes, &tm_w2, &full[s], slice0 * 128, (2 * jt + 1) * 128, expert);
+                    } else {
+                        tma_load_3d(st, &tm_w2, &full[s], slice0 * 128, jt * 128, expert);
+                        tma_load_3d(st + kTileBytes, &tm_w2, &full[s], (slice0 + 1) * 128, jt * 128, expert);
+                    }
+                    mbar_arrive_n(&full[s], GATHER_THREADS);
                 }
-                mbar_arrive_n(&full[s], 64);
                 if (++s == S) { s = 0; ph ^= 1; }
             }
         }
+    } else {
+        // ------------------------------------------------------------------ token-row gather (5 warps)
+        // Row group j (4 token rows x 128 B, one cp.async of the warp) belongs to gather warp j % 5: 7 groups for
+        // the first two warps, 6 for the others.  Lane l copies 16-byte piece l & 7 of row 4j + (l >> 3).
+        constexpr int GROUPS = kTmRows / 4;
+        constexpr int MAXG = (GROUPS + kTmGatherWarps - 1) / kTmGatherWarps;
+        const int gw = warp == W_G0 ? 0 : warp - W_G1 + 1;
+        const int ch = lane & 7;
+        uint32_t src16[MAXG];
+        uint32_t dst[MAXG];
+#pragma unroll
+        for (int i = 0; i < MAXG; ++i) {
+            const int grp = gw + kTmGatherWarps * i;
+            const int row = 4 * grp + (lane >> 3);
+            const int idx = mblock * p.block_m + row;
+            src16[i] = 0xFFFFFFFFu;
+            dst[i] = 0xFFFFFFFFu;                  // no such group for this warp
+            if (grp < GROUPS) {
+                dst[i] = row * 128 + ((ch ^ (row & 7)) << 4);
+                if (row < p.block_m && idx < p.sorted_num) {
+                    const int pid = p.sorted_token_ids[idx];
+                    if (pid >= 0 && pid < p.M * p.top_k)
+                        src16[i] = static_cast<uint32_t>((static_cast<size_t>(pid / p.top_k) * p.K) >> 4);
+                }
+            }
+        }
+        int s = 0;
+        uint32_t ph = 0;
+        int kc = 0;
+        for (int it = 0; it < UPI; ++it) {
+            if (!mbar_wait(&empty[s], ph ^ 1, abort_flag, p.status, 31, it)) break;
+            const uint32_t base = smem_u32(smem + s * L.stage_bytes + 2 * kTileBytes);
+            const uint8_t* col = p.x + kc * 128 + ch * 16;
+#pragma unroll
+            for (int i = 0; i < MAXG; ++i) {
+                if (dst[i] != 0xFFFFFFFFu) {
+                    const bool v = src16[i] != 0xFFFFFFFFu;
+                    const uint8_t* src = v ? col + (static_cast<size_t>(src16[i]) << 4) : p.x;
+                    cp_async_16(base + dst[i], src, v ? 16u : 0u);
+                }
+            }
+            cp_async_mbar_arrive_noinc(&full[s]);      // arrives when this thread's copies have landed
+            if (++s == S) { s = 0; ph ^= 1; }
+            if (++kc == KC) kc = 0;
+        }
+        cp_async_wait_all();                        // nothing of this thread may still be in flight at exit
     }
     } else {
         // ====================================================================== epilogue: thread = token
@@ -282,8 +330,22 @@ fused_moe_w8a8_up_down_sm100_tokmajor_kernel(const __grid_constant__ CUtensorMap
         }
         named_bar_sync(1, EPI_THREADS);
 
+        // Token scales come from global memory four chunks at a time, four to eight chunks ahead of their use
+        // (the next slice starts over at chunk 0 of the same row).  Nothing in the chunk loop may wait for
+        // these loads: the hand-offs below are relaxed arrivals (a default, releasing arrival would first wait
+        // for this thread's outstanding loads, i.e. a trip to L2 per chunk).
         const float* xs_row = p.x_scale + static_cast<size_t>(valid ? row : 0) * KC;
-        float sx_next = valid ? xs_row[0] : 0.f;
+        auto xs_at = [&](int c) {
+            while (c >= KC) c -= KC;
+            const float v = ld_global_nc_f32_pinned(xs_row + c);
+            return valid ? v : 0.f;
+        };
+        float sx_cur[4], sx_nxt[4];
+#pragma unroll
+        for (int j = 0; j < 4; ++j) {
+            sx_cur[j] = xs_at(j);
+            sx_nxt[j] = xs_at(4 + j);
+        }
 
         // accumulators of this token: 8 groups of (8 gate, 8 up) columns = 64 intermediate columns
         float acc[128];
@@ -294,19 +356,24 @@ fused_moe_w8a8_up_down_sm100_tokmajor_kernel(const __grid_constant__ CUtensorMap
         const uint32_t tlane = tmem_base + (static_cast<uint32_t>(q * 32) << 16);
         bool ok = true;
         int es = 0;
-        int kc = 0, sl = 0;
         uint32_t xph = 0;
-        // ---- up-projection: promote each K chunk with its scales (reference :915-933)
-        for (int it = 0; it < UPI && ok; ++it) {
+        // ---- up-projection: promote each K chunk with its scales (reference :915-933).  The chunk loop is kept
+        // small and contiguous (the slice-end code follows it instead of sitting inside it).
+        for (int sl = 0, it = 0; sl < SPC && ok; ++sl) {
+        for (int kc = 0; kc < KC; ++kc, ++it) {
             const int b = it & 1;
             const uint32_t aph = (it >> 1) & 1;
-            const float sx = sx_next;
-            {
-                const int nk = kc + 1 == KC ? 0 : kc + 1;
-                sx_next = valid ? xs_row[nk] : 0.f;          // prefetch the next chunk's token scale
+            if ((it & 3) == 0 && it > 0) {
+#pragma unroll
+                for (int j = 0; j < 4; ++j) {
+                    sx_cur[j] = sx_nxt[j];
+                    sx_nxt[j] = xs_at(kc + 4 + j);
+                }
             }
+            const int j4 = it & 3;
+            const float sx = j4 == 0 ? sx_cur[0] : j4 == 1 ? sx_cur[1] : j4 == 2 ? sx_cur[2] : sx_cur[3];
             if (!mbar_wait(&acc_full[b], aph, abort_flag, p.status, 40, it)) { ok = false; break; }
-            if (etid == 0) mbar_arrive(&empty[es]);
+            if (etid == 0) mbar_arrive_relaxed(&empty[es]);
             if (++es == S) es = 0;
             tc_fence_after();
             if (etid == 0) AMOE_STAMP(3, it);
@@ -330,10 +397,10 @@ fused_moe_w8a8_up_down_sm100_tokmajor_kernel(const __grid_constant__ CUtensorMap
             }
             tc_fence_before();
             __syncwarp();
-            if (lane == 0) mbar_arrive(&acc_empty[b]);
+            if (lane == 0) mbar_arrive_relaxed(&acc_empty[b]);
             if (etid == 0) AMOE_STAMP(4, it);
-
-            if (++kc == KC) {
+        }
+            if (ok) {
                 // ---- end of a slice: SwiGLU, amax over the slice's 128 columns (64 here + 64 in the partner
                 //      warpgroup's thread of the same token), fp8 re-quantisation (reference :936-1005)
                 float amax = 0.f;
@@ -351,7 +418,7 @@ fused_moe_w8a8_up_down_sm100_tokmajor_kernel(const __grid_constant__ CUtensorMap
                 amaxx[hh * kTmRows + t] = __float_as_uint(amax);
                 __syncwarp();
                 if (lane == 0) mbar_arrive(&xchg[0]);
-                if (!mbar_wait(&xchg[0], xph, abort_flag, p.status, 42, it)) ok = false;
+                if (!mbar_wait(&xchg[0], xph, abort_flag, p.status, 42, sl)) ok = false;
                 xph ^= 1;
                 amax = fmaxf(amax, __uint_as_float(amaxx[(hh ^ 1) * kTmRows + t]));
                 const float s_h = fmaxf(amax, 1e-10f) * (1.0f / 448.0f);
@@ -377,8 +444,6 @@ fused_moe_w8a8_up_down_sm100_tokmajor_kernel(const __grid_constant__ CUtensorMap
 #pragma unroll
                 for (int j = 0; j < 128; ++j) acc[j] = 0.f;
                 fence_proxy_async_smem();
-                kc = 0;
-                ++sl;
             }
         }
         named_bar_sync(1, EPI_THREADS);
@@ -390,7 +455,10 @@ fused_moe_w8a8_up_down_sm100_tokmajor_kernel(const __grid_constant__ CUtensorMap
         // a private staging tile: afterwards one instruction covers four token rows x 128 contiguous bytes
         // (whole lines), which is what the reduction path of the memory system handles best.  (Handing each
         // row to the bulk-copy engine instead - cp.reduce.async.bulk, 128 B per lane - measured 14 % slower.)
-        uint8_t* stg = smem + L.stage_out + warp * kStgWarpBytes;
+        // staging tiles: the token-row part of the ring slots is idle in this phase (three tiles per slot);
+        // a ring of fewer than three slots has room for a dedicated area
+        uint8_t* stg = L.stage_out != kStgAliased ? smem + L.stage_out + warp * kStgWarpBytes
+                                                  : smem + (warp / 3) * L.stage_bytes + 2 * kTileBytes + (warp % 3) * kStgWarpBytes;
         const int my_row = valid ? row : p.M;
         auto reduce_64 = [&](const float (&y)[64], int col0) {
 #pragma unroll
@@ -414,68 +482,64 @@ fused_moe_w8a8_up_down_sm100_tokmajor_kernel(const __grid_constant__ CUtensorMap
             }
             __syncwarp();
         };
+        // The two warpgroups take alternate iterations: while one is held up issuing its reductions (an SM
+        // passes only about 22 bytes of them per cycle) the other reads its accumulator and converts, so the
+        // reduction path stays busy.  A warpgroup therefore handles all columns of its iteration, in parts of
+        // 64 hidden columns: SPC = 2 -> 2 parts of hidden tile jt (columns [0,128) of the buffer are slice 0's
+        // partial sums, [128,256) slice 1's); SPC = 1 -> 4 parts covering hidden tiles 2jt and 2jt+1.
+        constexpr int PARTS = SPC == 1 ? 4 : 2;
+        const bool wg_lead = q == 0 && lane == 0;
         for (int jt = 0; jt < ND && ok; ++jt) {
             const int it = UPI + jt;
             const int b = it & 1;
             const uint32_t aph = (it >> 1) & 1;
-            if (!mbar_wait(&acc_full[b], aph, abort_flag, p.status, 41, it)) { ok = false; break; }
-            if (etid == 0) mbar_arrive_relaxed(&empty[es]);
+            const int slot = es;
             if (++es == S) es = 0;
+            if ((jt & 1) != hh) continue;
+            if (!mbar_wait(&acc_full[b], aph, abort_flag, p.status, 41, it)) { ok = false; break; }
+            if (wg_lead) mbar_arrive_relaxed(&empty[slot]);
             tc_fence_after();
-            if (etid == 0) AMOE_STAMP(3, it);
-            if constexpr (SPC == 1) {
-                // this warpgroup owns hidden tile 2jt + hh (accumulator columns [hh*128, +128))
-                const int tile = 2 * jt + hh;
+            if (wg_lead) AMOE_STAMP(3, it);
+#pragma unroll
+            for (int part = 0; part < PARTS; ++part) {
+                const int tile = SPC == 1 ? 2 * jt + (part >> 1) : jt;
                 const bool live = warp_valid && tile < KC;
-                uint32_t v[128];
+                float y[64];
                 if (live) {
-                    const uint32_t tb = tlane + b * 256 + hh * 128;
+                    const uint32_t tb = tlane + b * 256 + part * 64;
+                    if constexpr (SPC == 1) {
+                        uint32_t v[64];
 #pragma unroll
-                    for (int c0 = 0; c0 < 128; c0 += 16)
-                        tmem_ld16(tb + c0, *reinterpret_cast<uint32_t(*)[16]>(&v[c0]));
-                    tmem_ld_wait();
-                }
-                tc_fence_before();
-                __syncwarp();
-                if (lane == 0) mbar_arrive_relaxed(&acc_empty[b]);
-                if (etid == 0) AMOE_STAMP(4, it);
-                if (live) {
-                    const float f = sw2[tile] * fac[0];
+                        for (int c0 = 0; c0 < 64; c0 += 16)
+                            tmem_ld16(tb + c0, *reinterpret_cast<uint32_t(*)[16]>(&v[c0]));
+                        tmem_ld_wait();
+                        const float f = sw2[tile] * fac[0];
 #pragma unroll
-                    for (int half = 0; half < 2; ++half) {
-                        float y[64];
+                        for (int e = 0; e < 64; ++e) y[e] = __uint_as_float(v[e]) * f;
+                    } else {
+                        uint32_t va[64], vb[64];
 #pragma unroll
-                        for (int e = 0; e < 64; ++e) y[e] = __uint_as_float(v[64 * half + e]) * f;
-                        reduce_64(y, tile * 128 + 64 * half);
+                        for (int c0 = 0; c0 < 64; c0 += 16) {
+                            tmem_ld16(tb + c0, *reinterpret_cast<uint32_t(*)[16]>(&va[c0]));
+                            tmem_ld16(tb + 128 + c0, *reinterpret_cast<uint32_t(*)[16]>(&vb[c0]));
+                        }
+                        tmem_ld_wait();
+                        const float fa = sw2[jt] * fac[0], fb = sw2[KC + jt] * fac[SPC - 1];
+#pragma unroll
+                        for (int e = 0; e < 64; ++e)
+                            y[e] = fmaf(__uint_as_float(va[e]), fa, __uint_as_float(vb[e]) * fb);
                     }
                 }
-            } else {
-                // columns [0,128) = slice 0 partial sums of hidden tile jt, [128,256) = slice 1 partial sums;
-                // this warpgroup owns hidden columns [hh*64, +64) of the tile
-                uint32_t va[64], vb[64];
-                if (warp_valid) {
-                    const uint32_t tb = tlane + b * 256 + hh * 64;
-#pragma unroll
-                    for (int c0 = 0; c0 < 64; c0 += 16) {
-                        tmem_ld16(tb + c0, *reinterpret_cast<uint32_t(*)[16]>(&va[c0]));
-                        tmem_ld16(tb + 128 + c0, *reinterpret_cast<uint32_t(*)[16]>(&vb[c0]));
-                    }
-                    tmem_ld_wait();
+                if (part == PARTS - 1) {
+                    // the buffer has been read completely: hand it back before the last reductions are issued
+                    tc_fence_before();
+                    __syncwarp();
+                    if (lane == 0) mbar_arrive_relaxed_n(&acc_empty[b], 2);   // 4 warps stand in for the barrier's 8
+                    if (wg_lead) AMOE_STAMP(4, it);
                 }
-                tc_fence_before();
-                __syncwarp();
-                if (lane == 0) mbar_arrive_relaxed(&acc_empty[b]);
-                if (etid == 0) AMOE_STAMP(4, it);
-                if (warp_valid) {
-                    const float fa = sw2[jt] * fac[0], fb = sw2[KC + jt] * fac[SPC - 1];
-                    float y[64];
-#pragma unroll
-                    for (int e = 0; e < 64; ++e)
-                        y[e] = fmaf(__uint_as_float(va[e]), fa, __uint_as_float(vb[e]) * fb);
-                    reduce_64(y, jt * 128 + hh * 64);
-                }
+                if (live) reduce_64(y, (SPC == 1 ? tile * 128 + (part & 1) * 64 : jt * 128 + part * 64));
             }
-            if (etid == 0) AMOE_STAMP(5, it);
+            if (wg_lead) AMOE_STAMP(5, it);
         }
     }
 

@@ -194,7 +194,7 @@ int launch_tokmajor(const CUtensorMap& mw, const CUtensorMap& mw2, const amoe::M
         CUDA_TRY(cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, kMaxDynSmem));
         configured_smem[dev] = kMaxDynSmem;
     }
-    kern<<<grid, 384, smem_bytes, stream>>>(mw, mw2, p);
+    kern<<<grid, amoe::kTmThreads, smem_bytes, stream>>>(mw, mw2, p);
     CUDA_TRY(cudaGetLastError());
     return ALPHA_MOE_OK;
 }

@@ -47,6 +47,9 @@ __device__ __forceinline__ void mbar_arrive(uint64_t* bar) {
 __device__ __forceinline__ void mbar_arrive_relaxed(uint64_t* bar) {
     asm volatile("mbarrier.arrive.relaxed.cta.shared::cta.b64 _, [%0];" ::"r"(smem_u32(bar)) : "memory");
 }
+__device__ __forceinline__ void mbar_arrive_relaxed_n(uint64_t* bar, uint32_t n) {
+    asm volatile("mbarrier.arrive.relaxed.cta.shared::cta.b64 _, [%0], %1;" ::"r"(smem_u32(bar)), "r"(n) : "memory");
+}
 __device__ __forceinline__ void mbar_arrive_expect_tx(uint64_t* bar, uint32_t bytes) {
     asm volatile("mbarrier.arrive.expect_tx.shared::cta.b64 _, [%0], %1;" ::"r"(smem_u32(bar)), "r"(bytes)
                  : "memory");
@@ -68,6 +71,8 @@ constexpr long long kWaitLimitCycles = 2000000000LL;
 
 // Bounded wait.  `abort_flag` is a CTA-shared word: once any thread of the CTA gives up, every
 // other waiter of that CTA returns false at its next poll, so the CTA unwinds as a whole.
+// (Kept inline: a device function call inside a role that has resized its register budget with
+// setmaxnreg does not get through register allocation.)
 __device__ __forceinline__ bool mbar_wait(uint64_t* bar, uint32_t parity, volatile int* abort_flag,
                                           KernelStatus* status, int where, int iter) {
     if (mbar_try_wait(bar, parity)) return true;
@@ -145,6 +150,15 @@ __device__ __forceinline__ bool mbar_wait_cluster(uint64_t* bar, uint32_t parity
             return false;
         }
     }
+}
+
+// Global load that stays where it is written: the compiler does not move a volatile asm across the
+// other volatile asms (waits, arrivals, TMEM loads), so a prefetch into registers is really issued early
+// instead of being sunk to its first use to save registers.
+__device__ __forceinline__ float ld_global_nc_f32_pinned(const float* p) {
+    float v;
+    asm volatile("ld.global.nc.f32 %0, [%1];" : "=f"(v) : "l"(p));
+    return v;
 }
 
 // --------------------------------------------------------------------------------------------- proxies
