@@ -344,34 +344,65 @@ def main():
         return step_ms, kern_ms, inp, knobs
 
     def time_e2e(m, steps, warmup):
-        """Same step through the public operator with HOST inputs: pinned x / scales / routing are
-        copied to the device, the layer runs, `out` is copied back - all inside the timed region."""
+        """Same step through the public operator with HOST inputs: every step copies its pinned x / scales /
+        routing to the device, runs the layer and copies `out` back, all inside the timed region.  The three
+        stages of consecutive steps run on three streams over two sets of buffers (copy-in of step i+1 and
+        copy-out of step i-1 overlap the layer of step i), as a serving loop would issue them."""
         inp, d, out, _, (bm, bn, wn, st) = prepare(m)
         host = {"x": inp["x"].cpu().pin_memory(), "x_scale": inp["x_scale"].cpu().pin_memory(),
                 "topk_weights": inp["topk_weights"].pin_memory(), "sid": inp["sid"].pin_memory(),
                 "eid": inp["eid"].pin_memory(), "npp": inp["npp"].pin_memory()}
-        dbuf = {k: torch.empty_like(v, device=dev) for k, v in host.items()}
-        out_host = torch.empty(m, K, dtype=torch.bfloat16).pin_memory()
+        depth = 2
+        dbuf = [{k: torch.empty_like(v, device=dev) for k, v in host.items()} for _ in range(depth)]
+        outs = [out] + [torch.empty_like(out) for _ in range(depth - 1)]
+        out_host = [torch.empty(m, K, dtype=torch.bfloat16).pin_memory() for _ in range(depth)]
         h2d = sum(v.numel() * v.element_size() for v in host.values())
-        d2h = out_host.numel() * out_host.element_size()
+        d2h = out_host[0].numel() * out_host[0].element_size()
+        s_in, s_run, s_out = torch.cuda.Stream(), torch.cuda.Stream(), torch.cuda.Stream()
+        ev_in = [torch.cuda.Event() for _ in range(depth)]
+        ev_run = [torch.cuda.Event() for _ in range(depth)]
+        ev_out = [torch.cuda.Event() for _ in range(depth)]
+        main = torch.cuda.current_stream()
 
-        def step():
-            for k, v in host.items():
-                dbuf[k].copy_(v, non_blocking=True)
-            out.zero_()
-            op(dbuf["x"], dbuf["x_scale"], wl.w, wl.w_scale, wl.w2, wl.w2_scale, dbuf["sid"], dbuf["eid"],
-               dbuf["npp"], dbuf["topk_weights"], out, TOP_K, bm, bn, wn, st, SCALING)
-            if world > 1:
-                dist.all_reduce(out)
-            out_host.copy_(out, non_blocking=True)
-        for _ in range(warmup):
-            step()
+        def step(i):
+            j = i % depth
+            with torch.cuda.stream(s_in):
+                s_in.wait_event(ev_run[j])            # the layer that last read this input set has finished
+                for k, v in host.items():
+                    dbuf[j][k].copy_(v, non_blocking=True)
+                ev_in[j].record(s_in)
+            with torch.cuda.stream(s_run):
+                s_run.wait_event(ev_in[j])
+                s_run.wait_event(ev_out[j])           # the previous result in this output buffer has been copied out
+                outs[j].zero_()
+                op(dbuf[j]["x"], dbuf[j]["x_scale"], wl.w, wl.w_scale, wl.w2, wl.w2_scale, dbuf[j]["sid"],
+                   dbuf[j]["eid"], dbuf[j]["npp"], dbuf[j]["topk_weights"], outs[j], TOP_K, bm, bn, wn, st, SCALING)
+                if world > 1:
+                    dist.all_reduce(outs[j])
+                ev_run[j].record(s_run)
+            with torch.cuda.stream(s_out):
+                s_out.wait_event(ev_run[j])
+                out_host[j].copy_(outs[j], non_blocking=True)
+                ev_out[j].record(s_out)
+
+        def drain():
+            for s_ in (s_in, s_run, s_out):
+                main.wait_stream(s_)
+
+        for s_ in (s_in, s_run, s_out):
+            s_.wait_stream(main)
+        for i in range(warmup):
+            step(i)
+        drain()
         barrier()
         e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
-        e0.record()
-        for _ in range(steps):
-            step()
-        e1.record()
+        e0.record(main)
+        for s_ in (s_in, s_run, s_out):
+            s_.wait_event(e0)
+        for i in range(steps):
+            step(warmup + i)
+        drain()
+        e1.record(main)
         barrier()
         ms = e0.elapsed_time(e1) / steps
         if world > 1:
@@ -443,7 +474,8 @@ def main():
                          "frac_fp8_tensor": flops_per_gpu / (kern_ms * 1e-3) / 1e12 / fp8_peak,
                          "t_hbm_us": t_hbm * 1e6, "t_fp8_us": t_fp8 * 1e6},
             "e2e": {"value": flops_job / (e2e_ms * 1e-3) / 1e12, "unit": "TFLOP/s", "ms_per_step": e2e_ms,
-                    "h2d_bytes_per_step": h2d, "d2h_bytes_per_step": d2h},
+                    "h2d_bytes_per_step": h2d, "d2h_bytes_per_step": d2h,
+                    "pipeline": "copy-in / layer / copy-out of consecutive steps on three streams, two buffer sets"},
             "gpu_launches": args.steps,
             "clocks": clocks, "kernel_status": list(status), "sweep": sweep,
         }
