@@ -85,7 +85,7 @@ __host__ __device__ inline SmemPlan smem_plan(int bmp, int s, int kc, int spc, i
     p.tokrow = o;    o += bmp * 4;
     p.topkw = o;     o += bmp * 4;
     p.tokscale = o;  o += spc * bmp * 4;
-    p.amax = o;      o += bmp * 16;
+    p.amax = o;      o += bmp * 8;
     p.part = o;      o += ksplit > 1 ? 2 * bmp * 128 * 4 : 0;
     p.bars = o;      o += (2 * s + 10) * 8;
     p.misc = o;      o += 16;
@@ -93,11 +93,14 @@ __host__ __device__ inline SmemPlan smem_plan(int bmp, int s, int kc, int spc, i
     return p;
 }
 
-template <int BMP, int SPC>
-__global__ void __launch_bounds__(128 * (BMP >= 64 ? 2 : 1) + 128, BMP <= 32 ? 2 : 1)
+// EW = epilogue warpgroups.  BMP = 64 exists in two shapes: EW = 2 (one CTA per SM, deep ring) and EW = 1, whose
+// 256 threads and two-slot ring let two CTAs share an SM, so that one CTA's waits (accumulator hand-offs, the
+// switch between the two phases) are filled by the other CTA's work.
+template <int BMP, int SPC, int EW = (BMP >= 64 ? 2 : 1)>
+__global__ void __launch_bounds__(128 * EW + 128, (BMP <= 32 || (BMP == 64 && EW == 1)) ? 2 : 1)
 fused_moe_w8a8_up_down_sm100_kernel(const __grid_constant__ CUtensorMap tm_w,
                                     const __grid_constant__ CUtensorMap tm_w2, const MoeParams p) {
-    constexpr int NEPI_WG = BMP >= 64 ? 2 : 1;   // epilogue warpgroups; each owns BMP/NEPI_WG token columns
+    constexpr int NEPI_WG = EW;                  // epilogue warpgroups; each owns BMP/NEPI_WG token columns
     constexpr int NC = BMP / NEPI_WG;
     constexpr int EPI_THREADS = 128 * NEPI_WG;
     constexpr int W_G0 = 4 * NEPI_WG, W_MMA0 = W_G0 + 2;   // control warpgroup: gather, gather, UMMA, UMMA
@@ -159,7 +162,7 @@ fused_moe_w8a8_up_down_sm100_kernel(const __grid_constant__ CUtensorMap tm_w,
     int* tokrow = reinterpret_cast<int*>(smem + L.tokrow);            // [BMP] row of x/out, or M if padding
     float* topkw = reinterpret_cast<float*>(smem + L.topkw);          // [BMP]
     float* tokscale = reinterpret_cast<float*>(smem + L.tokscale);    // [SPC][BMP] s_h * topk_weight * scaling
-    uint32_t* amax_part = reinterpret_cast<uint32_t*>(smem + L.amax); // [BMP][4] per-warp |h| maxima
+    uint16_t* amax_part = reinterpret_cast<uint16_t*>(smem + L.amax); // [BMP][4] per-warp |h| maxima: |h| is a bf16 value, so the upper half of its fp32 pattern is exact
     uint64_t* full = reinterpret_cast<uint64_t*>(smem + L.bars);      // slot filled: TMA bytes + 64 gather threads
     uint64_t* empty = full + S;                                       // slot free again
     uint64_t* acc_full = empty + S;
@@ -207,7 +210,7 @@ fused_moe_w8a8_up_down_sm100_kernel(const __grid_constant__ CUtensorMap tm_w,
     // ====================================================================== control warpgroup
     // The widest variant keeps 2 x 64 accumulators per epilogue thread: it moves registers from this
     // warpgroup to the two epilogue warpgroups.
-    if constexpr (BMP == 128) setmaxnreg_dec<64>();
+    if constexpr (NC >= 64) setmaxnreg_dec<64>();
     if (warp >= W_MMA0) {
         // ------------------------------------------------------------------ UMMA issuers (even / odd chunks)
         if (lane == 0) {
@@ -340,7 +343,7 @@ fused_moe_w8a8_up_down_sm100_kernel(const __grid_constant__ CUtensorMap tm_w,
     }
     } else {
         // ====================================================================== epilogue warpgroups
-        if constexpr (BMP == 128) setmaxnreg_inc<216>();
+        if constexpr (NC >= 64) setmaxnreg_inc<(EW == 1 ? 192 : 216)>();
         const int q = warp & 3;              // TMEM lane quarter this warp may read
         const int hh = warp >> 2;            // which part of the token columns
         const int r = q * 32 + lane;         // weight row inside the tile = TMEM lane
@@ -490,7 +493,7 @@ fused_moe_w8a8_up_down_sm100_kernel(const __grid_constant__ CUtensorMap tm_w,
                         const float h = bf16_round(__fdividef(g, 1.0f + __expf(-g)) * u);
                         accg[j] = h;
                         const uint32_t a = __reduce_max_sync(0xFFFFFFFFu, __float_as_uint(fabsf(h)));
-                        if (lane == 0) amax_part[(hh * NC + j) * 4 + q] = a;
+                        if (lane == 0) amax_part[(hh * NC + j) * 4 + q] = static_cast<uint16_t>(a >> 16);
                     }
                     // exchange of the four warps' maxima through a (bounded) mbarrier rather than bar.sync, so
                     // that a warp that gave up on a wait can never leave the others parked at a hardware barrier
@@ -504,8 +507,9 @@ fused_moe_w8a8_up_down_sm100_kernel(const __grid_constant__ CUtensorMap tm_w,
                         const int col = hh * NC + j;
                         const uint32_t hoff = col * 128 + ((((r >> 4) ^ (col & 7)) << 4) | (r & 15));
                         if (j < NJ) {
-                            const uint4 pm = *reinterpret_cast<const uint4*>(amax_part + col * 4);
-                            const float amax = __uint_as_float(max(max(pm.x, pm.y), max(pm.z, pm.w)));
+                            const uint2 pm = *reinterpret_cast<const uint2*>(amax_part + col * 4);
+                            const float amax = __uint_as_float(
+                                max(max(pm.x & 0xFFFFu, pm.x >> 16), max(pm.y & 0xFFFFu, pm.y >> 16)) << 16);
                             const float s_h = fmaxf(amax, 1e-10f) * (1.0f / 448.0f);
                             const float qv = fminf(fmaxf(__fdividef(accg[j], s_h), -448.0f), 448.0f);
                             hq_sl[hoff] = static_cast<uint8_t>(__nv_cvt_float_to_fp8(qv, __NV_SATFINITE, __NV_E4M3));

@@ -126,6 +126,7 @@ int get_maps(int device, const void* w, const void* w2, int E, int N, int K, con
 }
 
 constexpr int kMaxDynSmem = 232448;  // 227 KB opt-in limit per CTA on sm_100
+constexpr int kPairDynSmem = 115712;  // what each of two co-resident CTAs may use (228 KB per SM, 1 KB reserved per CTA)
 
 int padded_block_m(int block_m) { return block_m <= 16 ? 16 : block_m <= 32 ? 32 : block_m <= 64 ? 64 : 128; }
 
@@ -150,10 +151,10 @@ int plan(int K, int block_m, int stages, int spc, int ksplit, int* depth, int* b
     return fail(ALPHA_MOE_E_ARG, "K=%d block_m=%d does not fit in shared memory even with one stage", K, block_m);
 }
 
-template <int BMP, int SPC>
+template <int BMP, int SPC, int EW = (BMP >= 64 ? 2 : 1)>
 int launch_variant(const CUtensorMap& mw, const CUtensorMap& mw2, const amoe::MoeParams& p, int grid, int smem_bytes,
                    cudaStream_t stream) {
-    auto kern = amoe::fused_moe_w8a8_up_down_sm100_kernel<BMP, SPC>;
+    auto kern = amoe::fused_moe_w8a8_up_down_sm100_kernel<BMP, SPC, EW>;
     static int configured_smem[64] = {0};   // per device: largest dynamic smem size already opted in
     int dev = 0;
     CUDA_TRY(cudaGetDevice(&dev));
@@ -161,7 +162,7 @@ int launch_variant(const CUtensorMap& mw, const CUtensorMap& mw2, const amoe::Mo
         CUDA_TRY(cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, kMaxDynSmem));
         configured_smem[dev] = kMaxDynSmem;
     }
-    constexpr int threads = 128 * (BMP >= 64 ? 2 : 1) + 128;
+    constexpr int threads = 128 * EW + 128;
     if (p.ksplit > 1) {
         cudaLaunchConfig_t cfg = {};
         cfg.gridDim = dim3(static_cast<unsigned>(grid));
@@ -289,6 +290,9 @@ int alpha_moe_b200_fused_moe_w8a8_up_down(const void* x, const float* x_scale, c
     if (grid > 0x7FFFFFFFLL) return fail(ALPHA_MOE_E_ARG, "grid too large");
     cudaStream_t st = static_cast<cudaStream_t>(stream);
     const int g = static_cast<int>(grid);
+    // A 64-wide tile with a ring of at most two slots runs the single-warpgroup shape, two CTAs per SM
+    // (227 KB per SM less 1 KB reserved per CTA leaves 113 KB of dynamic shared memory for each).
+    const bool pair64 = bmp == 64 && depth <= 2 && smem_bytes <= kPairDynSmem;
     if (token_major(block_m)) {
         return spc == 1 ? launch_tokmajor<1>(maps->w, maps->w2, p, g, smem_bytes, st)
                         : launch_tokmajor<2>(maps->w, maps->w2, p, g, smem_bytes, st);
@@ -297,14 +301,16 @@ int alpha_moe_b200_fused_moe_w8a8_up_down(const void* x, const float* x_scale, c
         switch (bmp) {
             case 16: return launch_variant<16, 1>(maps->w, maps->w2, p, g, smem_bytes, st);
             case 32: return launch_variant<32, 1>(maps->w, maps->w2, p, g, smem_bytes, st);
-            case 64: return launch_variant<64, 1>(maps->w, maps->w2, p, g, smem_bytes, st);
+            case 64: return pair64 ? launch_variant<64, 1, 1>(maps->w, maps->w2, p, g, smem_bytes, st)
+                                   : launch_variant<64, 1>(maps->w, maps->w2, p, g, smem_bytes, st);
             default: return launch_variant<128, 1>(maps->w, maps->w2, p, g, smem_bytes, st);
         }
     }
     switch (bmp) {
         case 16: return launch_variant<16, 2>(maps->w, maps->w2, p, g, smem_bytes, st);
         case 32: return launch_variant<32, 2>(maps->w, maps->w2, p, g, smem_bytes, st);
-        case 64: return launch_variant<64, 2>(maps->w, maps->w2, p, g, smem_bytes, st);
+        case 64: return pair64 ? launch_variant<64, 2, 1>(maps->w, maps->w2, p, g, smem_bytes, st)
+                               : launch_variant<64, 2>(maps->w, maps->w2, p, g, smem_bytes, st);
         default: return launch_variant<128, 2>(maps->w, maps->w2, p, g, smem_bytes, st);
     }
 }

@@ -85,6 +85,15 @@ def test_shapes(e, k, inter, m, top_k, bm):
     check_close(run_capi(case, bm, 64, 4, 3), ref, tag=f"E{e} K{k} I{inter} M{m}")
 
 
+@pytest.mark.parametrize("bm,bn,wn,stages", [(64, 64, 4, 2), (64, 32, 8, 2), (48, 64, 4, 1), (64, 64, 4, 3)])
+def test_sixty_four_wide_blocks_two_ctas_per_sm(bm, bn, wn, stages):
+    """Blocks of 33..64 assignments with a ring of at most two slots run the single-warpgroup shape of the
+    weight-major kernel (two CTAs per SM); deeper rings run the two-warpgroup shape.  Both against the oracle,
+    with full blocks, a ragged tail and more CTAs than one wave."""
+    case = orc.make_case(24, 2048, 256, 900, 6, seed=64 + stages, shared=True, scaling=2.5)
+    check_close(run_capi(case, bm, bn, wn, stages), orc.run_oracle(case, bm), tag=f"bm={bm} bn={bn} st={stages}")
+
+
 def test_skewed_routing_with_empty_experts():
     """Zipf(1.2) routing: several experts receive nothing, a few receive >10% of the tokens, so the
     schedule has empty experts, multi-block experts and ragged padding."""
