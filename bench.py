@@ -289,7 +289,19 @@ def main():
     dev = torch.device("cuda", local_rank)
     if world > 1:
         os.environ.setdefault("MASTER_ADDR", "127.0.0.1")
-        dist.init_process_group("nccl", device_id=dev)
+        # NCCL prints its version banner on stdout while the communicator comes up (when NCCL_DEBUG asks for
+        # one); stdout must carry the one JSON line only, so it points at stderr until the first collective is done
+        sys.stdout.flush()
+        saved_stdout = os.dup(1)
+        os.dup2(2, 1)
+        try:
+            dist.init_process_group("nccl", device_id=dev)
+            dist.barrier()
+            torch.cuda.synchronize()
+        finally:
+            sys.stdout.flush()
+            os.dup2(saved_stdout, 1)
+            os.close(saved_stdout)
 
     import alpha_moe  # noqa: F401  registers torch.ops.alpha_moe.fused_moe_w8a8_up_down
     from alpha_moe_b200 import capi
