@@ -71,7 +71,7 @@ constexpr long long kWaitLimitCycles = 2000000000LL;
 
 // Bounded wait.  `abort_flag` is a CTA-shared word: once any thread of the CTA gives up, every
 // other waiter of that CTA returns false at its next poll, so the CTA unwinds as a whole.
-// (Kept inline: a device function call inside a role that has resized its register budget with
+// (Kept inline: a device function call inside a role that has resized its register allotment with
 // setmaxnreg does not get through register allocation.)
 __device__ __forceinline__ bool mbar_wait(uint64_t* bar, uint32_t parity, volatile int* abort_flag,
                                           KernelStatus* status, int where, int iter) {

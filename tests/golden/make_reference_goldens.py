@@ -1,6 +1,6 @@
-"""Generates the golden fixtures of this directory.  Run once, in a container that has the
-reference checkout (default /root/reference, or $ALPHA_MOE_REFERENCE); the fixtures are committed
-so that the tests never read the reference at run time.
+"""Generates the golden fixtures of this directory.  Run once, where a checkout of the reference
+(Aleph-Alpha/Alpha-MoE) is at hand: `ALPHA_MOE_REFERENCE=<checkout> python make_reference_goldens.py`.
+The fixtures are committed so that the tests never read the reference at run time.
 
   ref_interleave.npz     outputs of the reference's alpha_moe_python.utils.interleave_tensor
                          (imported from the reference) on fixed integer inputs, rep = 8 / 1 / 2
@@ -22,7 +22,9 @@ import torch
 HERE = os.path.dirname(os.path.abspath(__file__))
 ROOT = os.path.dirname(os.path.dirname(HERE))
 sys.path.insert(0, ROOT)
-REF = os.environ.get("ALPHA_MOE_REFERENCE", "/root/reference")
+REF = os.environ.get("ALPHA_MOE_REFERENCE")
+if not REF or not os.path.isdir(REF):
+    raise SystemExit("set ALPHA_MOE_REFERENCE to a checkout of the reference repository")
 
 
 def load_reference_utils():
