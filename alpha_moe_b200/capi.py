@@ -35,6 +35,8 @@ lib.alpha_moe_b200_align_workspace_bytes.restype = ctypes.c_int64
 lib.alpha_moe_b200_align_workspace_bytes.argtypes = [_i, _i]
 lib.alpha_moe_b200_per_token_group_quant_fp8.restype = _i
 lib.alpha_moe_b200_per_token_group_quant_fp8.argtypes = [_vp, _vp, _vp, _i, _i, _i, _vp]
+lib.alpha_moe_b200_fused_experts.argtypes = [_vp] * 9 + [_i] * 5 + [_vp] * 4 + [_i] * 4 + [_f, _vp]
+lib.alpha_moe_b200_fused_experts.restype = _i
 lib.alpha_moe_b200_last_error.restype = ctypes.c_char_p
 lib.alpha_moe_b200_version.restype = ctypes.c_char_p
 
@@ -83,6 +85,16 @@ def align_workspace_bytes(numel: int, num_experts: int) -> int:
 def per_token_group_quant_fp8(x_bf16, x_fp8, x_scale, M, K, zero_src=False, stream=0) -> None:
     """Raw call: device addresses (ints)."""
     _check(lib.alpha_moe_b200_per_token_group_quant_fp8(x_bf16, x_fp8, x_scale, M, K, int(zero_src), stream))
+
+
+def fused_experts(hidden_states, x_fp8, x_scale, w, w_scale, w2, w2_scale, topk_ids, topk_weights, top_k, M, K, N,
+                  num_experts, sorted_token_ids, expert_ids, num_tokens_post_padded, align_workspace, block_m, block_n,
+                  warp_n, stages, scaling_factor, stream=0) -> None:
+    """Quantise + clear + schedule + fused operator in one call (device addresses as integers)."""
+    _check(lib.alpha_moe_b200_fused_experts(hidden_states, x_fp8, x_scale, w, w_scale, w2, w2_scale, topk_ids,
+                                            topk_weights, top_k, M, K, N, num_experts, sorted_token_ids, expert_ids,
+                                            num_tokens_post_padded, align_workspace, block_m, block_n, warp_n, stages,
+                                            scaling_factor, stream))
 
 
 def read_status(reset: bool = False):

@@ -347,6 +347,33 @@ int alpha_moe_b200_plan(int K, int block_m, int block_n, int stages, int32_t* ou
     return ALPHA_MOE_OK;
 }
 
+int alpha_moe_b200_fused_experts(void* hidden_states, void* x_fp8, float* x_scale, const void* w,
+                                 const float* w_scale, const void* w2, const float* w2_scale,
+                                 const int32_t* topk_ids, const float* topk_weights, int top_k, int M, int K, int N,
+                                 int num_experts, int32_t* sorted_token_ids, int32_t* expert_ids,
+                                 int32_t* num_tokens_post_padded, void* align_workspace, int block_m, int block_n,
+                                 int warp_n, int stages, float scaling_factor, void* stream) {
+    if (!hidden_states || !x_fp8 || !x_scale || !topk_ids || !sorted_token_ids || !expert_ids || !num_tokens_post_padded)
+        return fail(ALPHA_MOE_E_ARG, "null pointer argument");
+    if (M <= 0 || top_k <= 0 || num_experts <= 0) return fail(ALPHA_MOE_E_ARG, "M, top_k and num_experts must be positive");
+    if (block_m < 8 || block_m > 128 || block_m % 8 != 0) return fail(ALPHA_MOE_E_ARG, "bad block_m %d", block_m);
+    const long long numel = static_cast<long long>(M) * top_k;
+    const long long sorted_num = numel + static_cast<long long>(num_experts) * (block_m - 1);
+    if (sorted_num > 0x7FFFFFFFLL) return fail(ALPHA_MOE_E_ARG, "schedule too long for int32");
+    // extra/sglang.patch:30-31: quantise, then clear the buffer the layer accumulates into
+    if (int rc = alpha_moe_b200_per_token_group_quant_fp8(hidden_states, x_fp8, x_scale, M, K, 1, stream)) return rc;
+    // :33-35
+    if (int rc = alpha_moe_b200_moe_align_block_size(topk_ids, static_cast<int>(numel), num_experts, block_m,
+                                                      sorted_token_ids, expert_ids, num_tokens_post_padded,
+                                                      align_workspace, stream))
+        return rc;
+    // :38-40
+    return alpha_moe_b200_fused_moe_w8a8_up_down(x_fp8, x_scale, w, w_scale, w2, w2_scale, hidden_states, sorted_token_ids,
+                                                 expert_ids, num_tokens_post_padded, topk_weights, top_k, M, K, N,
+                                                 num_experts, static_cast<int>(sorted_num), block_m, block_n, warp_n,
+                                                 stages, scaling_factor, stream);
+}
+
 #ifdef AMOE_TRACE
 void alpha_moe_b200_debug_set_trace(long long* buf, int block) {
     g_trace = buf;

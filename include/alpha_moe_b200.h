@@ -78,6 +78,21 @@ int alpha_moe_b200_moe_align_block_size_noalloc(const int32_t* topk_ids, int num
 int alpha_moe_b200_per_token_group_quant_fp8(void* x_bf16, void* x_fp8, float* x_scale, int M, int K,
                                              int zero_src, void* stream);
 
+/* The whole call-site sequence of the reference's serving patch as one call (extra/sglang.patch:25-40, the body
+ * it gives fused_experts_impl): quantise the bf16 activations per token and 128-group, clear them (the layer's
+ * output accumulates into the same buffer), build the block schedule for `block_m`, run the fused operator.
+ * hidden_states: bf16 [M,K], activations on entry, layer output on return.  Scratch, all caller-owned device
+ * memory: x_fp8 [M,K] bytes, x_scale [M,K/128] f32, sorted_token_ids [M*top_k + num_experts*(block_m-1)] i32,
+ * expert_ids [ceil(that / block_m)] i32, num_tokens_post_padded [1] i32, align_workspace of
+ * alpha_moe_b200_align_workspace_bytes(M*top_k, num_experts) bytes (may be NULL when that is 0).
+ * Everything is enqueued on `stream`; nothing is allocated.  Error codes as for the single steps. */
+int alpha_moe_b200_fused_experts(void* hidden_states, void* x_fp8, float* x_scale, const void* w,
+                                 const float* w_scale, const void* w2, const float* w2_scale,
+                                 const int32_t* topk_ids, const float* topk_weights, int top_k, int M, int K, int N,
+                                 int num_experts, int32_t* sorted_token_ids, int32_t* expert_ids,
+                                 int32_t* num_tokens_post_padded, void* align_workspace, int block_m, int block_n,
+                                 int warp_n, int stages, float scaling_factor, void* stream);
+
 /* Reads (and optionally clears) the status word of the current device: out4 = {code, block, where, iter};
  * code 0 means no kernel wait has ever run out.  Synchronises the device. */
 int alpha_moe_b200_read_status(int32_t* out4, int reset);

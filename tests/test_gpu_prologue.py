@@ -85,3 +85,36 @@ def test_call_site_sequence_end_to_end():
                                                s_ids, e_ids, n_pad, wts.cuda(), hs, top_k, 16, 32, 8, 3, 2.5)
     torch.cuda.synchronize()
     assert orc.rel_l2(hs.cpu(), ref) <= 2e-2
+
+
+@pytest.mark.parametrize("m,conf", [(50, {"block_m": 16, "block_n": 32, "warp_n": 8, "stages": 3}),
+                                     (300, {"block_m": 128, "block_n": 64, "warp_n": 4, "stages": 3})])
+def test_fused_experts_single_call_matches_the_step_by_step_sequence(m, conf, tmp_path):
+    """alpha_moe_b200.layer.fused_experts_impl (one C-ABI call for the body of the reference's patched
+    fused_experts_impl, extra/sglang.patch:25-40) against the oracle, with the knobs given directly and
+    through a table file + ALPHA_MOE_CONFIG-style look-up."""
+    import json
+    from alpha_moe_b200.layer import fused_experts_impl
+    e, k, inter, top_k = 16, 1024, 256, 4
+    g = torch.Generator().manual_seed(5 + m)
+    w, w_scale, w2, w2_scale = orc.make_weights(e, k, inter, g)
+    hidden = torch.randn(m, k, generator=g).to(torch.bfloat16)
+    ids, wts = orc.route_topk(torch.randn(m, e, generator=g), top_k)
+    xq, xs = orc.quant_token_groups(hidden)
+    bm = conf["block_m"]
+    sid, eid, npp = orc.moe_align_block_size(ids, bm, e)
+    ref = orc.fused_moe_w8a8_up_down_oracle(xq, xs, w, w_scale, w2, w2_scale, sid, eid, npp, wts, top_k, bm, 2.5)
+    dw = [t.cuda() for t in (w, w_scale, w2, w2_scale)]
+
+    hs = hidden.cuda()
+    out = fused_experts_impl(hs, *dw, wts.cuda(), ids.cuda(), routed_scaling_factor=2.5, config=conf)
+    torch.cuda.synchronize()
+    assert out.data_ptr() == hs.data_ptr()            # result in place, as at the reference's call site
+    assert orc.rel_l2(hs.cpu(), ref) <= 2e-2
+
+    table = tmp_path / "moe.json"
+    table.write_text(json.dumps({str(m): conf}))
+    hs2 = hidden.cuda()
+    fused_experts_impl(hs2, *dw, wts.cuda(), ids.cuda(), routed_scaling_factor=2.5, config=str(table))
+    torch.cuda.synchronize()
+    assert torch.equal(hs2.cpu(), hs.cpu()) or orc.rel_l2(hs2.cpu(), hs.cpu()) <= 1e-2   # reduction order may differ

@@ -89,6 +89,20 @@ def test_capi_rejects_bad_arguments_without_a_gpu():
             call(**bad)
 
 
+def test_fused_experts_entry_rejects_bad_arguments_without_a_gpu():
+    """The single-call layer entry validates before it enqueues anything."""
+    from alpha_moe_b200 import capi
+    p = 0x1000
+    base = dict(hidden_states=p, x_fp8=p, x_scale=p, w=p, w_scale=p, w2=p, w2_scale=p, topk_ids=p, topk_weights=p,
+                top_k=2, M=4, K=512, N=256, num_experts=8, sorted_token_ids=p, expert_ids=p,
+                num_tokens_post_padded=p, align_workspace=0, block_m=16, block_n=32, warp_n=8, stages=3,
+                scaling_factor=1.0)
+    for bad, msg in ((dict(hidden_states=0), "null"), (dict(topk_ids=0), "null"), (dict(M=0), "positive"),
+                     (dict(block_m=12), "block_m"), (dict(block_m=200), "block_m"), (dict(K=500), "multiple of 128")):
+        with pytest.raises(capi.AlphaMoeError, match=msg):
+            capi.fused_experts(*dict(base, **bad).values())
+
+
 def test_plan_fits_shared_memory_for_every_knob():
     from alpha_moe_b200 import capi
     for k in (128, 2048, 4096, 7168):
