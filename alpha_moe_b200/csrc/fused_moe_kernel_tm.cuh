@@ -34,7 +34,7 @@ constexpr int kStgWarpBytes = 32 * kStgPitch;      // one warp's staging tile
 constexpr uint32_t kStgAliased = 0xFFFFFFFFu;      // SmemPlanTm::stage_out when the staging tiles alias the ring
 
 struct SmemPlanTm {
-    uint32_t stage_bytes, hq, stage_out, swg, swu, sw2, amaxx, bars, misc, total;
+    uint32_t stage_bytes, hq, stage_out, swg, swu, sw2, amaxx, xs, bars, misc, total;
 };
 __host__ __device__ inline SmemPlanTm smem_plan_tm(int s, int kc, int spc) {
     SmemPlanTm p;
@@ -49,6 +49,7 @@ __host__ __device__ inline SmemPlanTm smem_plan_tm(int s, int kc, int spc) {
     p.sw2 = o;    o += spc * kc * 4;
     o = (o + 15u) & ~15u;
     p.amaxx = o;  o += 2 * kTmRows * 4;
+    p.xs = o;     o += kc * kTmRows * 4;      // token scales [K chunk][token]
     p.bars = o;   o += (2 * s + 7) * 8;
     p.misc = o;   o += 16;
     p.total = o;
@@ -108,6 +109,7 @@ fused_moe_w8a8_up_down_sm100_tokmajor_kernel(const __grid_constant__ CUtensorMap
     float* swu = reinterpret_cast<float*>(smem + L.swu);
     float* sw2 = reinterpret_cast<float*>(smem + L.sw2);
     uint32_t* amaxx = reinterpret_cast<uint32_t*>(smem + L.amaxx);    // [2][128] per-thread |h| maxima of each column half
+    float* xs = reinterpret_cast<float*>(smem + L.xs);                // [KC][128] token scales (0 for padding rows)
     uint64_t* full = reinterpret_cast<uint64_t*>(smem + L.bars);
     uint64_t* empty = full + S;
     uint64_t* acc_full = empty + S;
@@ -330,22 +332,14 @@ fused_moe_w8a8_up_down_sm100_tokmajor_kernel(const __grid_constant__ CUtensorMap
         }
         named_bar_sync(1, EPI_THREADS);
 
-        // Token scales come from global memory four chunks at a time, four to eight chunks ahead of their use
-        // (the next slice starts over at chunk 0 of the same row).  Nothing in the chunk loop may wait for
-        // these loads: the hand-offs below are relaxed arrivals (a default, releasing arrival would first wait
-        // for this thread's outstanding loads, i.e. a trip to L2 per chunk).
-        const float* xs_row = p.x_scale + static_cast<size_t>(valid ? row : 0) * KC;
-        auto xs_at = [&](int c) {
-            while (c >= KC) c -= KC;
-            const float v = ld_global_nc_f32_pinned(xs_row + c);
-            return valid ? v : 0.f;
-        };
-        float sx_cur[4], sx_nxt[4];
-#pragma unroll
-        for (int j = 0; j < 4; ++j) {
-            sx_cur[j] = xs_at(j);
-            sx_nxt[j] = xs_at(4 + j);
+        // Token scales go to shared memory once (each warpgroup fetches one half of the K chunks of its tokens): the
+        // chunk loop then holds no global load, whose latency a releasing hand-off would have to wait out.
+        {
+            const float* xs_row = p.x_scale + static_cast<size_t>(valid ? row : 0) * KC;
+            const int c_begin = hh * (KC >> 1), c_end = hh == 0 ? (KC >> 1) : KC;
+            for (int c = c_begin; c < c_end; ++c) xs[c * kTmRows + t] = valid ? xs_row[c] : 0.f;
         }
+        named_bar_sync(1, EPI_THREADS);
 
         // accumulators of this token: 8 groups of (8 gate, 8 up) columns = 64 intermediate columns
         float acc[128];
@@ -363,15 +357,7 @@ fused_moe_w8a8_up_down_sm100_tokmajor_kernel(const __grid_constant__ CUtensorMap
         for (int kc = 0; kc < KC; ++kc, ++it) {
             const int b = it & 1;
             const uint32_t aph = (it >> 1) & 1;
-            if ((it & 3) == 0 && it > 0) {
-#pragma unroll
-                for (int j = 0; j < 4; ++j) {
-                    sx_cur[j] = sx_nxt[j];
-                    sx_nxt[j] = xs_at(kc + 4 + j);
-                }
-            }
-            const int j4 = it & 3;
-            const float sx = j4 == 0 ? sx_cur[0] : j4 == 1 ? sx_cur[1] : j4 == 2 ? sx_cur[2] : sx_cur[3];
+            const float sx = xs[kc * kTmRows + t];
             if (!mbar_wait(&acc_full[b], aph, abort_flag, p.status, 40, it)) { ok = false; break; }
             if (etid == 0) mbar_arrive_relaxed(&empty[es]);
             if (++es == S) es = 0;

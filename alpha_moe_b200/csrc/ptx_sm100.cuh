@@ -152,15 +152,6 @@ __device__ __forceinline__ bool mbar_wait_cluster(uint64_t* bar, uint32_t parity
     }
 }
 
-// Global load that stays where it is written: the compiler does not move a volatile asm across the
-// other volatile asms (waits, arrivals, TMEM loads), so a prefetch into registers is really issued early
-// instead of being sunk to its first use to save registers.
-__device__ __forceinline__ float ld_global_nc_f32_pinned(const float* p) {
-    float v;
-    asm volatile("ld.global.nc.f32 %0, [%1];" : "=f"(v) : "l"(p));
-    return v;
-}
-
 // --------------------------------------------------------------------------------------------- proxies
 __device__ __forceinline__ void fence_proxy_async_smem() {
     asm volatile("fence.proxy.async.shared::cta;" ::: "memory");
