@@ -188,31 +188,57 @@ moe_align_single_kernel(const int32_t* ids, int numel, int E, int block, int32_t
 
 // ------------------------------------------------------------------------------------------------
 // Per-(token, 128-group) fp8 quantisation: scale = max(amax, 1e-10) / 448, q = e4m3_rn(clamp(x / scale)).
-// One warp per group: 4 bf16 per lane in, 4 fp8 per lane out; algorithmic traffic 3 bytes per element
-// (+ 2 when the source is zeroed).  IEEE divisions keep the result bit-identical to the CPU restatement.
+// Eight lanes per group, 16 elements per lane: two 16-byte loads in, one 16-byte store out (algorithmic traffic
+// 3 bytes per element, + 2 when the source is zeroed); a warp takes four consecutive groups per step and the grid
+// strides over the tensor.  IEEE divisions keep the result bit-identical to the CPU restatement.
 __global__ void __launch_bounds__(256)
 group_quant_fp8_kernel(__nv_bfloat16* x, uint8_t* q, float* scale, long long n_groups, int zero_src) {
-    const long long g = static_cast<long long>(blockIdx.x) * 8 + (threadIdx.x >> 5);
-    if (g >= n_groups) return;
     const int lane = threadIdx.x & 31;
-    uint2* src = reinterpret_cast<uint2*>(x + g * 128) + lane;
-    const uint2 raw = *src;
-    const __nv_bfloat162 a = *reinterpret_cast<const __nv_bfloat162*>(&raw.x);
-    const __nv_bfloat162 b = *reinterpret_cast<const __nv_bfloat162*>(&raw.y);
-    const float v[4] = {__low2float(a), __high2float(a), __low2float(b), __high2float(b)};
-    float amax = fmaxf(fmaxf(fabsf(v[0]), fabsf(v[1])), fmaxf(fabsf(v[2]), fabsf(v[3])));
+    const int sub = lane & 7;                   // 16-element piece of the group
+    const long long warp0 = static_cast<long long>(blockIdx.x) * 8 + (threadIdx.x >> 5);
+    const long long nwarps = static_cast<long long>(gridDim.x) * 8;
+    for (long long g0 = warp0 * 4; g0 < n_groups; g0 += nwarps * 4) {
+        const long long g = g0 + (lane >> 3);
+        const bool live = g < n_groups;
+        uint4* src = reinterpret_cast<uint4*>(x + (live ? g : 0) * 128 + sub * 16);
+        uint4 r0 = make_uint4(0u, 0u, 0u, 0u), r1 = r0;
+        if (live) {
+            r0 = src[0];
+            r1 = src[1];
+        }
+        const uint32_t w[8] = {r0.x, r0.y, r0.z, r0.w, r1.x, r1.y, r1.z, r1.w};
+        float v[16];
+        float amax = 0.f;
 #pragma unroll
-    for (int o = 16; o > 0; o >>= 1) amax = fmaxf(amax, __shfl_xor_sync(0xFFFFFFFFu, amax, o));
-    const float s = __fdiv_rn(fmaxf(amax, 1e-10f), 448.0f);
-    uint32_t packed = 0;
+        for (int i = 0; i < 8; ++i) {
+            const __nv_bfloat162 a = *reinterpret_cast<const __nv_bfloat162*>(&w[i]);
+            v[2 * i] = __low2float(a);
+            v[2 * i + 1] = __high2float(a);
+            amax = fmaxf(amax, fmaxf(fabsf(v[2 * i]), fabsf(v[2 * i + 1])));
+        }
 #pragma unroll
-    for (int i = 0; i < 4; ++i) {
-        const float y = fminf(fmaxf(__fdiv_rn(v[i], s), -448.0f), 448.0f);
-        packed |= static_cast<uint32_t>(__nv_cvt_float_to_fp8(y, __NV_SATFINITE, __NV_E4M3)) << (8 * i);
+        for (int o = 4; o > 0; o >>= 1) amax = fmaxf(amax, __shfl_xor_sync(0xFFFFFFFFu, amax, o));
+        const float s = __fdiv_rn(fmaxf(amax, 1e-10f), 448.0f);
+        uint32_t out[4];
+#pragma unroll
+        for (int i = 0; i < 4; ++i) {
+            uint32_t packed = 0;
+#pragma unroll
+            for (int j = 0; j < 4; ++j) {
+                const float y = fminf(fmaxf(__fdiv_rn(v[4 * i + j], s), -448.0f), 448.0f);
+                packed |= static_cast<uint32_t>(__nv_cvt_float_to_fp8(y, __NV_SATFINITE, __NV_E4M3)) << (8 * j);
+            }
+            out[i] = packed;
+        }
+        if (live) {
+            *reinterpret_cast<uint4*>(q + g * 128 + sub * 16) = make_uint4(out[0], out[1], out[2], out[3]);
+            if (sub == 0) scale[g] = s;
+            if (zero_src) {
+                src[0] = make_uint4(0u, 0u, 0u, 0u);
+                src[1] = make_uint4(0u, 0u, 0u, 0u);
+            }
+        }
     }
-    reinterpret_cast<uint32_t*>(q + g * 128)[lane] = packed;
-    if (lane == 0) scale[g] = s;
-    if (zero_src) *src = make_uint2(0u, 0u);
 }
 
 // Scratch of the entry point that allocates nothing: the per-chunk histogram table lives here instead of
@@ -296,11 +322,15 @@ int alpha_moe_b200_per_token_group_quant_fp8(void* x_bf16, void* x_fp8, float* x
     using namespace amoe_aux;
     if (!x_bf16 || !x_fp8 || !x_scale) return fail(ALPHA_MOE_E_ARG, "null pointer argument");
     if (M <= 0 || K <= 0 || K % 128 != 0) return fail(ALPHA_MOE_E_ARG, "need M > 0 and K a positive multiple of 128");
-    if ((reinterpret_cast<uintptr_t>(x_bf16) & 7) || (reinterpret_cast<uintptr_t>(x_fp8) & 3))
-        return fail(ALPHA_MOE_E_ARG, "x_bf16 must be 8-byte aligned and x_fp8 4-byte aligned");
+    if ((reinterpret_cast<uintptr_t>(x_bf16) & 15) || (reinterpret_cast<uintptr_t>(x_fp8) & 15))
+        return fail(ALPHA_MOE_E_ARG, "x_bf16 and x_fp8 must be 16-byte aligned");
     const long long n_groups = static_cast<long long>(M) * (K / 128);
-    const long long blocks = (n_groups + 7) / 8;
-    if (blocks > 0x7FFFFFFFLL) return fail(ALPHA_MOE_E_ARG, "too many groups");
+    // 32 groups per block and step; enough blocks for eight per SM at most, the rest is covered by the stride
+    int dev = 0, sms = 0;
+    AUX_TRY(cudaGetDevice(&dev));
+    AUX_TRY(cudaDeviceGetAttribute(&sms, cudaDevAttrMultiProcessorCount, dev));
+    long long blocks = (n_groups + 31) / 32;
+    if (blocks > static_cast<long long>(sms) * 8) blocks = static_cast<long long>(sms) * 8;
     group_quant_fp8_kernel<<<static_cast<unsigned>(blocks), 256, 0, static_cast<cudaStream_t>(stream)>>>(
         static_cast<__nv_bfloat16*>(x_bf16), static_cast<uint8_t*>(x_fp8), x_scale, n_groups, zero_src);
     AUX_TRY(cudaGetLastError());

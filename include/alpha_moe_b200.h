@@ -74,7 +74,8 @@ int alpha_moe_b200_moe_align_block_size_noalloc(const int32_t* topk_ids, int num
 /* Replaces the external sglang_per_token_group_quant_fp8(x, 128) the reference calls before the
  * operator (jit_moe.py:142, extra/sglang.patch:30): bf16 [M,K] -> fp8 e4m3 [M,K] + f32 scale [M,K/128],
  * scale = max(amax,1e-10)/448.  If zero_src != 0 the bf16 source is zeroed after it has been read,
- * which is what the call site does next (extra/sglang.patch:31) because `out` aliases it. */
+ * which is what the call site does next (extra/sglang.patch:31) because `out` aliases it.
+ * x_bf16 and x_fp8 must be 16-byte aligned. */
 int alpha_moe_b200_per_token_group_quant_fp8(void* x_bf16, void* x_fp8, float* x_scale, int M, int K,
                                              int zero_src, void* stream);
 

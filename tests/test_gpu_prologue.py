@@ -43,7 +43,7 @@ def test_moe_align_duplicates_skew_and_out_of_range_ids():
     assert sorted(real.tolist()) == [i for i in range(flat.numel()) if 0 <= int(flat[i]) < 8]
 
 
-@pytest.mark.parametrize("m,k", [(1, 128), (3, 512), (64, 7168), (1000, 2048)])
+@pytest.mark.parametrize("m,k", [(1, 128), (3, 512), (64, 7168), (1000, 2048), (8192, 7168)])
 def test_group_quant_matches_oracle_bit_for_bit(m, k):
     from alpha_moe_b200.prologue import per_token_group_quant_fp8
     g = torch.Generator().manual_seed(m * 7 + k)
