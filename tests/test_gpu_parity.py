@@ -5,6 +5,7 @@ same seeded inputs.  Tolerances (floating point, bf16 output accumulated with at
   reference's own    : allclose(atol=2e-2, rtol=1e-1) under its own input distribution
                        (test/test_moe_correctness.py:47-48,106-110,147-155)
 """
+import dataclasses
 import os
 
 import numpy as np
@@ -185,3 +186,42 @@ def test_k_split_over_a_cluster_small_batches(ks, monkeypatch):
     # K with a chunk count that does not divide by ks, and an odd number of hidden tiles
     case = orc.make_case(8, 1152, 128, 2, 2, seed=9)
     check_close(run_capi(case, 16, 32, 8, 3), orc.run_oracle(case, 16), tag=f"ks={ks} K=1152")
+
+
+def test_every_token_to_one_expert_many_blocks_of_the_same_weights():
+    """Maximum imbalance: all assignments land on two experts, so one expert owns dozens of consecutive blocks
+    (narrow, 64-wide and token-major shapes)."""
+    case = orc.make_case(6, 1024, 256, 700, 2, seed=21, scaling=1.5)
+    ids = torch.zeros_like(case.topk_ids)
+    ids[:, 1] = 3
+    case = dataclasses.replace(case, topk_ids=ids.contiguous())
+    for bm, bn, wn, st in ((16, 32, 8, 3), (64, 64, 4, 2), (128, 64, 4, 3), (128, 32, 8, 2)):
+        check_close(run_capi(case, bm, bn, wn, st), orc.run_oracle(case, bm), tag=f"one expert bm={bm} bn={bn}")
+
+
+@pytest.mark.parametrize("e,k,inter,m,top_k,bm,bn,wn", [
+    (4, 128, 128, 150, 2, 128, 64, 4),     # a single K chunk and a single slice in the token-major kernel
+    (4, 128, 128, 150, 2, 64, 64, 4),      # same in the 64-wide shape (block_n = 64 falls back to one slice per CTA)
+    (4, 256, 384, 260, 3, 128, 64, 4),     # three slices: odd slice count, so one slice per CTA despite block_n = 64
+    (4, 2304, 256, 129, 2, 128, 64, 4),    # 18 K chunks, second block of every expert almost empty
+    (3, 640, 128, 9, 3, 72, 32, 8),        # fewer tokens than the block size, every token to every expert
+])
+def test_edge_shapes_of_the_wide_kernels(e, k, inter, m, top_k, bm, bn, wn):
+    case = orc.make_case(e, k, inter, m, top_k, seed=e * k + m, scaling=0.5)
+    check_close(run_capi(case, bm, bn, wn, 3), orc.run_oracle(case, bm), tag=f"E{e} K{k} I{inter} M{m} bm={bm}")
+
+
+def test_zero_and_negative_routing_weights_and_scales():
+    """topk_weights of zero cancel an assignment, negative ones and negative weight scales (the reference's own
+    generator produces them) flip signs; nothing in the kernel may assume positivity."""
+    case = orc.make_case(8, 512, 256, 90, 3, seed=33, scaling=2.0)
+    wts = case.topk_weights.clone()
+    wts[::3, 0] = 0.0
+    wts[1::3, 1] *= -1.0
+    ws = case.w_scale.clone()
+    ws[::2] *= -1.0
+    w2s = case.w2_scale.clone()
+    w2s[1::2] *= -1.0
+    case = dataclasses.replace(case, topk_weights=wts.contiguous(), w_scale=ws.contiguous(), w2_scale=w2s.contiguous())
+    for bm, bn, wn in ((16, 32, 8), (64, 64, 4), (128, 64, 4)):
+        check_close(run_capi(case, bm, bn, wn, 2), orc.run_oracle(case, bm), tag=f"signs bm={bm}")
