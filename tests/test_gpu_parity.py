@@ -225,3 +225,37 @@ def test_zero_and_negative_routing_weights_and_scales():
     case = dataclasses.replace(case, topk_weights=wts.contiguous(), w_scale=ws.contiguous(), w2_scale=w2s.contiguous())
     for bm, bn, wn in ((16, 32, 8), (64, 64, 4), (128, 64, 4)):
         check_close(run_capi(case, bm, bn, wn, 2), orc.run_oracle(case, bm), tag=f"signs bm={bm}")
+
+
+@pytest.mark.parametrize("m,bm,bn,wn,st", [(8, 16, 32, 8, 3), (300, 128, 64, 4, 3)])
+def test_operator_replays_from_a_cuda_graph(m, bm, bn, wn, st):
+    """Serving engines capture the decode step in a CUDA graph: after one eager call (which sets the kernel's
+    shared-memory attribute and builds the tensor maps) the operator is captured together with the clearing of
+    `out` and replayed; every replay must give the eager result (up to the order of the bf16 reductions)."""
+    import alpha_moe  # noqa: F401
+    case = orc.make_case(16, 1024, 256, m, 4, seed=70 + m, scaling=2.5)
+    d = to_device(case)
+    sid, eid, npp = [t.cuda() for t in case.schedule(bm)]
+    out = torch.zeros(m, 1024, dtype=torch.bfloat16, device="cuda")
+
+    def layer():
+        out.zero_()
+        torch.ops.alpha_moe.fused_moe_w8a8_up_down(d["x"], d["x_scale"], d["w"], d["w_scale"], d["w2"], d["w2_scale"],
+                                                   sid, eid, npp, d["topk_weights"], out, case.top_k, bm, bn, wn, st, 2.5)
+    layer()
+    torch.cuda.synchronize()
+    eager = out.clone()
+    check_close(eager.cpu(), orc.run_oracle(case, bm), tag="eager")
+    g = torch.cuda.CUDAGraph()
+    s = torch.cuda.Stream()
+    s.wait_stream(torch.cuda.current_stream())
+    with torch.cuda.stream(s):
+        layer()                      # warm-up on the capture stream
+        torch.cuda.synchronize()
+        with torch.cuda.graph(g, stream=s):
+            layer()
+    for _ in range(3):
+        out.fill_(7.0)               # the captured clear must take care of this
+        g.replay()
+        torch.cuda.synchronize()
+        assert orc.rel_l2(out.cpu(), eager.cpu()) <= 1e-2
