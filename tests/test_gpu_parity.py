@@ -105,16 +105,35 @@ def test_skewed_routing_with_empty_experts():
         check_close(run_capi(case, bm, 32, 8, 4), orc.run_oracle(case, bm), tag=f"zipf bm={bm}")
 
 
-def test_reference_input_distribution_and_literal_tolerance():
-    """The reference's own generator (duplicates of an expert inside a token included) and its own
-    pass criterion, against the faithful oracle."""
-    for m, e, n, k in ((8, 8, 256, 4096), (32, 37, 512, 7168), (128, 8, 512, 4096)):
-        case = orc.make_reference_style_case(m, e, n, k, 9)
-        for bm in (16, 8 if m >= 8 else 16):
-            ref = orc.run_oracle(case, bm).float()
-            got = run_capi(case, bm, 32, 8, 3).float()
-            assert torch.allclose(got, ref, atol=2e-2, rtol=1e-1), f"M={m} E={e} N={n} K={k} bm={bm}"
-            assert orc.rel_l2(got, ref) <= 2e-2
+# one knob tuple per kernel shape: 16/32/64-wide weight-major (64 in both its shapes), token-major with one and two slices
+_GRID_KNOBS = [(8, 32, 8, 3), (16, 64, 4, 5), (32, 32, 8, 2), (64, 64, 4, 2), (64, 32, 8, 4), (128, 64, 4, 3), (96, 32, 8, 2)]
+
+
+@pytest.mark.parametrize("e", [257, 8, 37])
+@pytest.mark.parametrize("n", [256, 512])
+@pytest.mark.parametrize("k", [7168, 4096])
+def test_reference_input_distribution_and_literal_tolerance(e, n, k):
+    """The reference's own sweep grid (test/test_moe_correctness.py:118-140: E in {257,8,37} x N in {256,512} x
+    K in {7168,4096} x M in {8,32,128,256}, top_k = 9), its own generator (duplicates of an expert inside a token
+    included, negative block scales) and its own pass criterion, against the faithful oracle.  Each case runs three
+    knob tuples, rotating so that every kernel shape meets every (E, N, K)."""
+    weights = None
+    for i, m in enumerate((8, 32, 128, 256)):
+        case = orc.make_reference_style_case(m, e, n, k, 9, seed=42 + m, weights=weights)
+        weights = (case.w, case.w_scale, case.w2, case.w2_scale)
+        dcase = to_device(case)
+        refs = {}
+        base = (i * 3 + e + n // 256 + k // 4096) % len(_GRID_KNOBS)
+        for j in range(3):
+            bm, bn, wn, st = _GRID_KNOBS[(base + j) % len(_GRID_KNOBS)]
+            if m < bm and bm != 16:          # the reference skips these too (:189-190)
+                bm, bn, wn, st = 16, bn, wn, st
+            if bm not in refs:
+                refs[bm] = orc.run_oracle(case, bm).float()
+            got = run_capi(case, bm, bn, wn, st, dcase=dcase).float()
+            tag = f"M={m} E={e} N={n} K={k} knobs={bm},{bn},{wn},{st}"
+            assert torch.allclose(got, refs[bm], atol=2e-2, rtol=1e-1), tag
+            assert orc.rel_l2(got, refs[bm]) <= 2e-2, tag
 
 
 def test_schedule_is_followed_and_padding_rows_untouched():
