@@ -26,7 +26,9 @@ lib.alpha_moe_b200_fused_moe_w8a8_up_down.argtypes = [_vp] * 11 + [_i] * 10 + [_
 lib.alpha_moe_b200_read_status.restype = _i
 lib.alpha_moe_b200_read_status.argtypes = [ctypes.POINTER(ctypes.c_int32), _i]
 lib.alpha_moe_b200_plan.restype = _i
-lib.alpha_moe_b200_plan.argtypes = [_i, _i, _i, _i, ctypes.POINTER(ctypes.c_int32)]
+lib.alpha_moe_b200_plan.argtypes = [_i] * 7 + [ctypes.POINTER(ctypes.c_int32)]
+lib.alpha_moe_b200_set_ksplit.restype = _i
+lib.alpha_moe_b200_set_ksplit.argtypes = [_i]
 lib.alpha_moe_b200_moe_align_block_size.restype = _i
 lib.alpha_moe_b200_moe_align_block_size.argtypes = [_vp, _i, _i, _i, _vp, _vp, _vp, _vp, _vp]
 lib.alpha_moe_b200_moe_align_block_size_noalloc.restype = _i
@@ -104,11 +106,18 @@ def read_status(reset: bool = False):
     return tuple(buf)
 
 
-def plan(K: int, block_m: int, stages: int, block_n: int = 32):
-    """(ring_depth, padded_block_m, dynamic_smem_bytes, slices_per_cta) the launcher would use."""
-    buf = (ctypes.c_int32 * 4)()
-    _check(lib.alpha_moe_b200_plan(K, block_m, block_n, stages, buf))
+def plan(K: int, block_m: int, stages: int, block_n: int = 32, N: int = 512, num_blocks: int = 1 << 20,
+         num_sms: int = 148):
+    """(ring_depth, padded_block_m, dynamic_smem_bytes, slices_per_cta, ksplit, kernel) the launcher uses;
+    kernel: 0 weight-major, 1 token-major."""
+    buf = (ctypes.c_int32 * 6)()
+    _check(lib.alpha_moe_b200_plan(K, N, block_m, block_n, stages, num_blocks, num_sms, buf))
     return tuple(buf)
+
+
+def set_ksplit(ksplit: int = 0) -> None:
+    """Tuning hook: CTAs per cluster along K for small batches (0 = automatic)."""
+    _check(lib.alpha_moe_b200_set_ksplit(ksplit))
 
 
 def version() -> str:

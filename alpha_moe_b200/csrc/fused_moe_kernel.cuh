@@ -460,10 +460,12 @@ fused_moe_w8a8_up_down_sm100_kernel(const __grid_constant__ CUtensorMap tm_w,
                     if (!mbar_wait(xsync, 0, abort_flag, p.status, 45, it)) ok = false;
                     if (etid < ks) mbar_arrive_cluster(mapa_shared(smem_u32(peer_ready), etid));
                     if (!mbar_wait_cluster(peer_ready, 0, abort_flag, p.status, 43, it)) ok = false;
+                    // After a wait that ran out, a peer may have left already: no peer's shared memory is read from
+                    // here on (this CTA is unwinding; its sums are not used any more).
                     const uint32_t my_part = smem_u32(part);
 #pragma unroll
                     for (int j = 0; j < NC; ++j) {
-                        if (j < my_ncols) {
+                        if (j < my_ncols && ok) {
                             float g = 0.f, u = 0.f;
                             for (int peer = 0; peer < ks; ++peer) {
                                 const uint32_t base = mapa_shared(my_part, peer);
@@ -477,7 +479,7 @@ fused_moe_w8a8_up_down_sm100_kernel(const __grid_constant__ CUtensorMap tm_w,
                     __syncwarp();
                     if (lane == 0) mbar_arrive(xsync);       // every thread of this CTA is done reading the peers
                     if (!mbar_wait(xsync, 1, abort_flag, p.status, 46, it)) ok = false;
-                    if (etid < ks) mbar_arrive_cluster(mapa_shared(smem_u32(peer_done), etid));
+                    if (etid < ks && ok) mbar_arrive_cluster(mapa_shared(smem_u32(peer_done), etid));
                 }
                 if (etid == 0) AMOE_STAMP(10, 1);
                 // ---- end of a slice: SwiGLU, per-token amax over the slice's 128 columns, fp8 re-quantisation

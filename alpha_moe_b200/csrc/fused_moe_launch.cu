@@ -8,6 +8,7 @@
 #include <cuda.h>
 #include <cuda_runtime.h>
 
+#include <atomic>
 #include <cstdarg>
 #include <cstdio>
 #include <cstdlib>
@@ -76,54 +77,57 @@ int get_encode_fn(EncodeTiledFn* out) {
     return ALPHA_MOE_OK;
 }
 
-struct MapPair {
-    CUtensorMap w, w2;
+struct MapSet {
+    CUtensorMap w, w2;      // boxes of 256 rows of w and of 128 rows of w2, each 128 bytes wide
 };
 using MapKey = std::tuple<int, const void*, const void*, int, int, int>;  // device, w, w2, E, N, K
 
-// Tensor maps depend only on the weight pointers and shapes, so a serving process encodes them
-// once per layer.  The cache is bounded; on overflow it is simply cleared.
-int get_maps(int device, const void* w, const void* w2, int E, int N, int K, const MapPair** out) {
-    static std::map<MapKey, MapPair> cache;
+int encode_map(EncodeTiledFn enc, CUtensorMap* m, const void* base, cuuint64_t inner, cuuint64_t rows, cuuint64_t experts,
+               cuuint32_t box_rows, const char* what) {
+    cuuint64_t dims[3] = {inner, rows, experts};
+    cuuint64_t strides[2] = {inner, rows * inner};
+    cuuint32_t box[3] = {128, box_rows, 1};
+    cuuint32_t estr[3] = {1, 1, 1};
+    CUresult r = enc(m, CU_TENSOR_MAP_DATA_TYPE_UINT8, 3, const_cast<void*>(base), dims, strides, box, estr,
+                     CU_TENSOR_MAP_INTERLEAVE_NONE, CU_TENSOR_MAP_SWIZZLE_128B, CU_TENSOR_MAP_L2_PROMOTION_L2_256B,
+                     CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE);
+    if (r != CUDA_SUCCESS) return fail(ALPHA_MOE_E_CUDA, "cuTensorMapEncodeTiled(%s) failed with CUresult %d", what, (int)r);
+    return ALPHA_MOE_OK;
+}
+
+// Tensor maps depend only on the weight pointers and shapes, so a serving process encodes them once per
+// layer.  The cache is bounded (cleared on overflow); the maps are handed out by value, under the lock, so
+// that no caller ever holds a pointer into it.
+int get_maps(int device, const void* w, const void* w2, int E, int N, int K, MapSet* out) {
+    static std::map<MapKey, MapSet> cache;
     static std::mutex mu;
     std::lock_guard<std::mutex> lock(mu);
     MapKey key{device, w, w2, E, N, K};
     auto it = cache.find(key);
     if (it != cache.end()) {
-        *out = &it->second;
+        *out = it->second;
         return ALPHA_MOE_OK;
     }
     EncodeTiledFn enc;
     if (int rc = get_encode_fn(&enc)) return rc;
-    MapPair mp;
-    const cuuint64_t I = static_cast<cuuint64_t>(N) / 2, Kk = K, Nn = N;
-    {
-        // w [E][N][K]: box = 256 consecutive (interleaved) rows x 128 bytes of K.
-        cuuint64_t dims[3] = {Kk, Nn, static_cast<cuuint64_t>(E)};
-        cuuint64_t strides[2] = {Kk, Nn * Kk};
-        cuuint32_t box[3] = {128, 256, 1};
-        cuuint32_t estr[3] = {1, 1, 1};
-        CUresult r = enc(&mp.w, CU_TENSOR_MAP_DATA_TYPE_UINT8, 3, const_cast<void*>(w), dims, strides, box, estr,
-                         CU_TENSOR_MAP_INTERLEAVE_NONE, CU_TENSOR_MAP_SWIZZLE_128B, CU_TENSOR_MAP_L2_PROMOTION_L2_256B,
-                         CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE);
-        if (r != CUDA_SUCCESS) return fail(ALPHA_MOE_E_CUDA, "cuTensorMapEncodeTiled(w) failed with CUresult %d", (int)r);
-    }
-    {
-        // w2 [E][K][I]: box = 128 hidden rows x 128 bytes of one intermediate slice; rows past K read zero.
-        cuuint64_t dims[3] = {I, Kk, static_cast<cuuint64_t>(E)};
-        cuuint64_t strides[2] = {I, Kk * I};
-        cuuint32_t box[3] = {128, 128, 1};
-        cuuint32_t estr[3] = {1, 1, 1};
-        CUresult r = enc(&mp.w2, CU_TENSOR_MAP_DATA_TYPE_UINT8, 3, const_cast<void*>(w2), dims, strides, box, estr,
-                         CU_TENSOR_MAP_INTERLEAVE_NONE, CU_TENSOR_MAP_SWIZZLE_128B, CU_TENSOR_MAP_L2_PROMOTION_L2_256B,
-                         CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE);
-        if (r != CUDA_SUCCESS) return fail(ALPHA_MOE_E_CUDA, "cuTensorMapEncodeTiled(w2) failed with CUresult %d", (int)r);
-    }
+    MapSet ms;
+    const cuuint64_t I = static_cast<cuuint64_t>(N) / 2, Kk = K, Nn = N, Ee = E;
+    // w [E][N][K]: box = consecutive (interleaved) rows x 128 bytes of K
+    if (int rc = encode_map(enc, &ms.w, w, Kk, Nn, Ee, 256, "w")) return rc;
+    // w2 [E][K][I]: box = hidden rows x 128 bytes of one intermediate slice; rows past K read zero
+    if (int rc = encode_map(enc, &ms.w2, w2, I, Kk, Ee, 128, "w2")) return rc;
     if (cache.size() > 4096) cache.clear();
-    auto ins = cache.emplace(key, mp);
-    *out = &ins.first->second;
+    cache.emplace(key, ms);
+    *out = ms;
     return ALPHA_MOE_OK;
 }
+
+// Facts about a device that never change, looked up once: the SM count and the address of the status word.
+struct DeviceFacts {
+    int sms = 0;
+    amoe::KernelStatus* status = nullptr;
+};
+constexpr int kMaxDevices = 64;
 
 constexpr int kMaxDynSmem = 232448;  // 227 KB opt-in limit per CTA on sm_100
 constexpr int kPairDynSmem = 115712;  // what each of two co-resident CTAs may use (228 KB per SM, 1 KB reserved per CTA)
@@ -151,17 +155,21 @@ int plan(int K, int block_m, int stages, int spc, int ksplit, int* depth, int* b
     return fail(ALPHA_MOE_E_ARG, "K=%d block_m=%d does not fit in shared memory even with one stage", K, block_m);
 }
 
+// Opts a kernel into the large dynamic shared-memory window once per device (atomically: several host threads
+// may launch at the same time).
+template <typename Kern>
+int ensure_smem_attr(Kern kern, std::atomic<int>* configured, int dev) {
+    if (dev < kMaxDevices && configured[dev].load(std::memory_order_acquire)) return ALPHA_MOE_OK;
+    CUDA_TRY(cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, kMaxDynSmem));
+    if (dev < kMaxDevices) configured[dev].store(1, std::memory_order_release);
+    return ALPHA_MOE_OK;
+}
+
 template <int BMP, int SPC, int EW = (BMP >= 64 ? 2 : 1)>
-int launch_variant(const CUtensorMap& mw, const CUtensorMap& mw2, const amoe::MoeParams& p, int grid, int smem_bytes,
-                   cudaStream_t stream) {
+int launch_variant(const MapSet& maps, const amoe::MoeParams& p, int grid, int smem_bytes, int dev, cudaStream_t stream) {
     auto kern = amoe::fused_moe_w8a8_up_down_sm100_kernel<BMP, SPC, EW>;
-    static int configured_smem[64] = {0};   // per device: largest dynamic smem size already opted in
-    int dev = 0;
-    CUDA_TRY(cudaGetDevice(&dev));
-    if (dev < 64 && configured_smem[dev] < smem_bytes) {
-        CUDA_TRY(cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, kMaxDynSmem));
-        configured_smem[dev] = kMaxDynSmem;
-    }
+    static std::atomic<int> configured[kMaxDevices];
+    if (int rc = ensure_smem_attr(kern, configured, dev)) return rc;
     constexpr int threads = 128 * EW + 128;
     if (p.ksplit > 1) {
         cudaLaunchConfig_t cfg = {};
@@ -176,28 +184,50 @@ int launch_variant(const CUtensorMap& mw, const CUtensorMap& mw2, const amoe::Mo
         attr.val.clusterDim.z = 1;
         cfg.attrs = &attr;
         cfg.numAttrs = 1;
-        CUDA_TRY(cudaLaunchKernelEx(&cfg, kern, mw, mw2, p));
+        CUDA_TRY(cudaLaunchKernelEx(&cfg, kern, maps.w, maps.w2, p));
         return ALPHA_MOE_OK;
     }
-    kern<<<grid, threads, smem_bytes, stream>>>(mw, mw2, p);
+    kern<<<grid, threads, smem_bytes, stream>>>(maps.w, maps.w2, p);
     CUDA_TRY(cudaGetLastError());
     return ALPHA_MOE_OK;
 }
 
 template <int SPC>
-int launch_tokmajor(const CUtensorMap& mw, const CUtensorMap& mw2, const amoe::MoeParams& p, int grid, int smem_bytes,
-                    cudaStream_t stream) {
+int launch_tokmajor(const MapSet& maps, const amoe::MoeParams& p, int grid, int smem_bytes, int dev, cudaStream_t stream) {
     auto kern = amoe::fused_moe_w8a8_up_down_sm100_tokmajor_kernel<SPC>;
-    static int configured_smem[64] = {0};
-    int dev = 0;
-    CUDA_TRY(cudaGetDevice(&dev));
-    if (dev < 64 && configured_smem[dev] < smem_bytes) {
-        CUDA_TRY(cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, kMaxDynSmem));
-        configured_smem[dev] = kMaxDynSmem;
-    }
-    kern<<<grid, amoe::kTmThreads, smem_bytes, stream>>>(mw, mw2, p);
+    static std::atomic<int> configured[kMaxDevices];
+    if (int rc = ensure_smem_attr(kern, configured, dev)) return rc;
+    kern<<<grid, amoe::kTmThreads, smem_bytes, stream>>>(maps.w, maps.w2, p);
     CUDA_TRY(cudaGetLastError());
     return ALPHA_MOE_OK;
+}
+
+int device_facts(int dev, DeviceFacts* out) {
+    static DeviceFacts facts[kMaxDevices];
+    static std::mutex mu;
+    std::lock_guard<std::mutex> lock(mu);
+    DeviceFacts local;
+    DeviceFacts& f = dev < kMaxDevices ? facts[dev] : local;
+    if (!f.status) {
+        CUDA_TRY(cudaDeviceGetAttribute(&f.sms, cudaDevAttrMultiProcessorCount, dev));
+        CUDA_TRY(cudaGetSymbolAddress(reinterpret_cast<void**>(&f.status), g_status));
+    }
+    *out = f;
+    return ALPHA_MOE_OK;
+}
+
+std::atomic<int> g_ksplit_override{0};     // 0 = automatic; set through alpha_moe_b200_set_ksplit (tuners, tests)
+
+// Clusters of 2 or 4 CTAs along K for small batches: as many as still fit one CTA per SM (narrow tile, one slice
+// per CTA only; 8 is accepted as an override but measured no faster than 4).
+int choose_ksplit(int block_m, int spc, long long nblocks, int N, int K, int sms) {
+    if (block_m > 32 || spc != 1) return 1;
+    int ksplit = 1;
+    const long long live_max = nblocks * (N / 256);
+    while (ksplit < 4 && live_max * ksplit * 2 <= sms && ksplit * 2 <= K / 128) ksplit *= 2;
+    const int v = g_ksplit_override.load(std::memory_order_relaxed);
+    if ((v == 1 || v == 2 || v == 4 || v == 8) && v <= K / 128) ksplit = v;
+    return ksplit;
 }
 
 }  // namespace
@@ -225,8 +255,15 @@ int alpha_moe_b200_fused_moe_w8a8_up_down(const void* x, const float* x_scale, c
         return fail(ALPHA_MOE_E_ARG, "block_m must be a multiple of 8 in 8..128, got %d", block_m);
     if ((reinterpret_cast<uintptr_t>(w) | reinterpret_cast<uintptr_t>(w2) | reinterpret_cast<uintptr_t>(x)) & 15)
         return fail(ALPHA_MOE_E_ARG, "x, w and w2 must be 16-byte aligned");
-    if (reinterpret_cast<uintptr_t>(out) & 3) return fail(ALPHA_MOE_E_ARG, "out must be 4-byte aligned");
+    // the token-major kernels accumulate with 16-byte vector reductions, the others with 4-byte ones
+    if (reinterpret_cast<uintptr_t>(out) & (token_major(block_m) ? 15 : 3))
+        return fail(ALPHA_MOE_E_ARG, "out must be %d-byte aligned for block_m=%d", token_major(block_m) ? 16 : 4, block_m);
     if (static_cast<long long>(M) * top_k > 0x7FFFFFFFLL) return fail(ALPHA_MOE_E_ARG, "M*top_k overflows int32");
+
+    int dev = 0;
+    CUDA_TRY(cudaGetDevice(&dev));
+    DeviceFacts facts;
+    if (int rc = device_facts(dev, &facts)) return rc;
 
     // block_n = 64 asks for the wide variant: one CTA owns two 128-column slices of the intermediate
     // dimension (one reduction per token and expert instead of two); it needs an even slice count.
@@ -234,31 +271,12 @@ int alpha_moe_b200_fused_moe_w8a8_up_down(const void* x, const float* x_scale, c
     // Live blocks never exceed the number of assignments, so no more CTAs than that are launched.
     long long nblocks = (static_cast<long long>(sorted_num) + block_m - 1) / block_m;
     if (nblocks > static_cast<long long>(M) * top_k) nblocks = static_cast<long long>(M) * top_k;
-    // Small batches activate few experts: split each (block, slice) over a cluster of 2 or 4 CTAs along K
-    // while the CTAs still fit one per SM (narrow tile, one slice per CTA only; 8 is accepted through
-    // ALPHA_MOE_KSPLIT but measured no faster than 4).
-    int ksplit = 1;
-    if (block_m <= 32 && spc == 1) {
-        int sms = 0, dev_now = 0;
-        CUDA_TRY(cudaGetDevice(&dev_now));
-        CUDA_TRY(cudaDeviceGetAttribute(&sms, cudaDevAttrMultiProcessorCount, dev_now));
-        const long long live_max = nblocks * (N / 256);
-        while (ksplit < 4 && live_max * ksplit * 2 <= sms && ksplit * 2 <= K / 128) ksplit *= 2;
-        if (const char* env = getenv("ALPHA_MOE_KSPLIT")) {
-            const int v = atoi(env);
-            if ((v == 1 || v == 2 || v == 4 || v == 8) && v <= K / 128) ksplit = v;
-        }
-    }
+    const int ksplit = choose_ksplit(block_m, spc, nblocks, N, K, facts.sms);
     int depth, bmp, smem_bytes;
     if (int rc = plan(K, block_m, stages, spc, ksplit, &depth, &bmp, &smem_bytes)) return rc;
 
-    int dev = 0;
-    CUDA_TRY(cudaGetDevice(&dev));
-    const MapPair* maps = nullptr;
+    MapSet maps;
     if (int rc = get_maps(dev, w, w2, num_experts, N, K, &maps)) return rc;
-
-    amoe::KernelStatus* status = nullptr;
-    CUDA_TRY(cudaGetSymbolAddress(reinterpret_cast<void**>(&status), g_status));
 
     amoe::MoeParams p;
     p.x = static_cast<const uint8_t*>(x);
@@ -280,7 +298,7 @@ int alpha_moe_b200_fused_moe_w8a8_up_down(const void* x, const float* x_scale, c
     p.stages = depth;
     p.ksplit = ksplit;
     p.scaling = scaling_factor;
-    p.status = status;
+    p.status = facts.status;
 #ifdef AMOE_TRACE
     p.trace = g_trace;
     p.trace_block = g_trace_block;
@@ -293,26 +311,30 @@ int alpha_moe_b200_fused_moe_w8a8_up_down(const void* x, const float* x_scale, c
     // A 64-wide tile with a ring of at most two slots runs the single-warpgroup shape, two CTAs per SM
     // (227 KB per SM less 1 KB reserved per CTA leaves 113 KB of dynamic shared memory for each).
     const bool pair64 = bmp == 64 && depth <= 2 && smem_bytes <= kPairDynSmem;
-    if (token_major(block_m)) {
-        return spc == 1 ? launch_tokmajor<1>(maps->w, maps->w2, p, g, smem_bytes, st)
-                        : launch_tokmajor<2>(maps->w, maps->w2, p, g, smem_bytes, st);
-    }
+    if (token_major(block_m))
+        return spc == 1 ? launch_tokmajor<1>(maps, p, g, smem_bytes, dev, st)
+                        : launch_tokmajor<2>(maps, p, g, smem_bytes, dev, st);
     if (spc == 1) {
         switch (bmp) {
-            case 16: return launch_variant<16, 1>(maps->w, maps->w2, p, g, smem_bytes, st);
-            case 32: return launch_variant<32, 1>(maps->w, maps->w2, p, g, smem_bytes, st);
-            case 64: return pair64 ? launch_variant<64, 1, 1>(maps->w, maps->w2, p, g, smem_bytes, st)
-                                   : launch_variant<64, 1>(maps->w, maps->w2, p, g, smem_bytes, st);
-            default: return launch_variant<128, 1>(maps->w, maps->w2, p, g, smem_bytes, st);
+            case 16: return launch_variant<16, 1>(maps, p, g, smem_bytes, dev, st);
+            case 32: return launch_variant<32, 1>(maps, p, g, smem_bytes, dev, st);
+            default: return pair64 ? launch_variant<64, 1, 1>(maps, p, g, smem_bytes, dev, st)
+                                   : launch_variant<64, 1>(maps, p, g, smem_bytes, dev, st);
         }
     }
     switch (bmp) {
-        case 16: return launch_variant<16, 2>(maps->w, maps->w2, p, g, smem_bytes, st);
-        case 32: return launch_variant<32, 2>(maps->w, maps->w2, p, g, smem_bytes, st);
-        case 64: return pair64 ? launch_variant<64, 2, 1>(maps->w, maps->w2, p, g, smem_bytes, st)
-                               : launch_variant<64, 2>(maps->w, maps->w2, p, g, smem_bytes, st);
-        default: return launch_variant<128, 2>(maps->w, maps->w2, p, g, smem_bytes, st);
+        case 16: return launch_variant<16, 2>(maps, p, g, smem_bytes, dev, st);
+        case 32: return launch_variant<32, 2>(maps, p, g, smem_bytes, dev, st);
+        default: return pair64 ? launch_variant<64, 2, 1>(maps, p, g, smem_bytes, dev, st)
+                               : launch_variant<64, 2>(maps, p, g, smem_bytes, dev, st);
     }
+}
+
+int alpha_moe_b200_set_ksplit(int ksplit) {
+    if (ksplit != 0 && ksplit != 1 && ksplit != 2 && ksplit != 4 && ksplit != 8)
+        return fail(ALPHA_MOE_E_ARG, "ksplit must be 0 (automatic), 1, 2, 4 or 8, got %d", ksplit);
+    g_ksplit_override.store(ksplit, std::memory_order_relaxed);
+    return ALPHA_MOE_OK;
 }
 
 int alpha_moe_b200_read_status(int32_t* out4, int reset) {
@@ -331,19 +353,25 @@ int alpha_moe_b200_read_status(int32_t* out4, int reset) {
     return ALPHA_MOE_OK;
 }
 
-int alpha_moe_b200_plan(int K, int block_m, int block_n, int stages, int32_t* out4) {
-    if (!out4) return fail(ALPHA_MOE_E_ARG, "out4 is null");
+int alpha_moe_b200_plan(int K, int N, int block_m, int block_n, int stages, int num_blocks, int num_sms,
+                        int32_t* out6) {
+    if (!out6) return fail(ALPHA_MOE_E_ARG, "out6 is null");
     if (K <= 0 || K % 128 != 0) return fail(ALPHA_MOE_E_ARG, "K dimension must be a multiple of 128 (K=%d)", K);
+    if (N <= 0 || N % 256 != 0) return fail(ALPHA_MOE_E_ARG, "N must be a multiple of 256 (N=%d)", N);
     if (block_m < 8 || block_m > 128 || block_m % 8 != 0) return fail(ALPHA_MOE_E_ARG, "bad block_m %d", block_m);
     if (block_n != 32 && block_n != 64) return fail(ALPHA_MOE_E_ARG, "block_n must be 32 or 64, got %d", block_n);
     if (stages < 1 || stages > 5) return fail(ALPHA_MOE_E_ARG, "stages must be in 1..5, got %d", stages);
-    const int spc = block_n == 64 ? 2 : 1;
+    if (num_blocks <= 0 || num_sms <= 0) return fail(ALPHA_MOE_E_ARG, "num_blocks and num_sms must be positive");
+    const int spc = (block_n == 64 && (N / 256) % 2 == 0) ? 2 : 1;
+    const int ksplit = choose_ksplit(block_m, spc, num_blocks, N, K, num_sms);
     int depth, bmp, smem_bytes;
-    if (int rc = plan(K, block_m, stages, spc, 1, &depth, &bmp, &smem_bytes)) return rc;
-    out4[0] = depth;
-    out4[1] = bmp;
-    out4[2] = smem_bytes;
-    out4[3] = spc;
+    if (int rc = plan(K, block_m, stages, spc, ksplit, &depth, &bmp, &smem_bytes)) return rc;
+    out6[0] = depth;
+    out6[1] = bmp;
+    out6[2] = smem_bytes;
+    out6[3] = spc;
+    out6[4] = ksplit;
+    out6[5] = token_major(block_m) ? 1 : 0;
     return ALPHA_MOE_OK;
 }
 

@@ -12,6 +12,37 @@ from . import capi
 from .utils import get_best_config
 
 
+def _check_layer_arguments(hidden_states, w1, w1_scale, w2, w2_scale, topk_weights, topk_ids) -> None:
+    """The checks the torch operator makes on its tensors (csrc/torch_interface.cpp:58-76 of the reference, plus
+    the dtype / device / shape checks this library's operator adds), made here before any raw pointer is taken:
+    this path goes straight to the C ABI, which sees only addresses."""
+    def need(cond, msg):
+        if not cond:
+            raise RuntimeError(msg)
+    need(hidden_states.dtype == torch.bfloat16 and hidden_states.dim() == 2 and hidden_states.is_contiguous(),
+         "hidden_states must be a contiguous 2-D bfloat16 tensor")
+    dev = hidden_states.device
+    m, k = hidden_states.shape
+    need(m > 0, "hidden_states must have at least one row")
+    need(k % 128 == 0, "K dimension must be a multiple of 128")
+    need(w1.dim() == 3 and w2.dim() == 3, "w1 must be [E, 2I, K] and w2 [E, K, I]")
+    e, n, kw = w1.shape
+    need(kw == k, "w1.size(2) must equal hidden_states.size(1)")
+    need(n % 256 == 0, "N (2 x intermediate size) must be a multiple of 256")
+    need(tuple(w2.shape) == (e, k, n // 2), "w2 must be [E, K, N/2]")
+    need(w1.dtype == torch.float8_e4m3fn and w2.dtype == torch.float8_e4m3fn, "w1 and w2 must be float8_e4m3fn")
+    need(tuple(w1_scale.shape) == (e, n // 128, k // 128), "w1_scale must be [E, N/128, K/128]")
+    need(tuple(w2_scale.shape) == (e, k // 128, n // 256), "w2_scale must be [E, K/128, N/256]")
+    need(w1_scale.dtype == torch.float32 and w2_scale.dtype == torch.float32, "weight scales must be float32")
+    need(topk_ids.dim() == 2 and topk_ids.shape[0] == m, "topk_ids must be [M, top_k]")
+    need(tuple(topk_weights.shape) == tuple(topk_ids.shape), "topk_weights must have the shape of topk_ids")
+    for name, t in (("w1", w1), ("w1_scale", w1_scale), ("w2", w2), ("w2_scale", w2_scale)):
+        need(t.is_contiguous(), f"{name} must be contiguous")
+    for name, t in (("w1", w1), ("w1_scale", w1_scale), ("w2", w2), ("w2_scale", w2_scale),
+                    ("topk_weights", topk_weights), ("topk_ids", topk_ids)):
+        need(t.device == dev, f"{name} must be on {dev}")
+
+
 def fused_experts_impl(hidden_states: torch.Tensor, w1: torch.Tensor, w1_scale: torch.Tensor, w2: torch.Tensor,
                        w2_scale: torch.Tensor, topk_weights: torch.Tensor, topk_ids: torch.Tensor,
                        routed_scaling_factor: float | None = None, block_shape=(128, 128),
@@ -21,9 +52,9 @@ def fused_experts_impl(hidden_states: torch.Tensor, w1: torch.Tensor, w1_scale: 
     topk_weights f32 [M,top_k].  `config`: a knob dict, a table path, or None for $ALPHA_MOE_CONFIG."""
     if tuple(block_shape) != (128, 128):
         raise ValueError("only 128 x 128 block scales are supported (the operator's scale layout)")
-    if not hidden_states.is_cuda or hidden_states.dtype != torch.bfloat16 or hidden_states.dim() != 2 \
-            or not hidden_states.is_contiguous():
-        raise RuntimeError("hidden_states must be a contiguous 2-D bfloat16 CUDA tensor")
+    _check_layer_arguments(hidden_states, w1, w1_scale, w2, w2_scale, topk_weights, topk_ids)
+    if not hidden_states.is_cuda:
+        raise RuntimeError("hidden_states must be a CUDA tensor (there is no CPU implementation)")
     m, k = hidden_states.shape
     e, n, _ = w1.shape
     top_k = topk_ids.shape[1]

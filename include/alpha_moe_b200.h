@@ -35,7 +35,8 @@ extern "C" {
  * (block_n,warp_n) in {(64,4),(32,8)}, 1 <= stages <= 5, block_m in {8,16,...,128}.
  * Here stages = depth of the shared-memory ring (lowered if it would not fit), and block_n = 64
  * selects the variant in which one CTA owns two 128-column slices of the intermediate dimension.
- * Requires K % 128 == 0, N % 256 == 0, 16-byte aligned w / w2 / x. */
+ * Requires K % 128 == 0, N % 256 == 0, 16-byte aligned w / w2 / x; `out` 4-byte aligned for block_m <= 64 and
+ * 16-byte aligned for block_m > 64 (those kernels accumulate with 16-byte vector reductions). */
 int alpha_moe_b200_fused_moe_w8a8_up_down(
     const void* x, const float* x_scale, const void* w, const float* w_scale, const void* w2,
     const float* w2_scale, void* out, const int32_t* sorted_token_ids, const int32_t* expert_ids,
@@ -98,10 +99,17 @@ int alpha_moe_b200_fused_experts(void* hidden_states, void* x_fp8, float* x_scal
  * code 0 means no kernel wait has ever run out.  Synchronises the device. */
 int alpha_moe_b200_read_status(int32_t* out4, int reset);
 
-/* What the launcher would use for these knobs; for tuners and tests.  out4 = {ring_depth,
- * padded_block_m, dynamic_smem_bytes, slices_per_cta (2 when block_n = 64 and N/256 is even)}.
- * No device work. */
-int alpha_moe_b200_plan(int K, int block_m, int block_n, int stages, int32_t* out4);
+/* What the launcher uses for a problem and a knob tuple; for tuners and tests.  It runs the launcher's own
+ * planning code.  num_blocks = live upper bound of schedule blocks, min(ceil(sorted_num / block_m), M * top_k);
+ * num_sms = SM count of the device (148 on B200).  out6 = {ring_depth, padded_block_m, dynamic_smem_bytes,
+ * slices_per_cta (2 when block_n = 64 and N/256 is even), ksplit (CTAs per cluster along K, small batches),
+ * kernel (0 weight-major, 1 token-major)}.  No device work. */
+int alpha_moe_b200_plan(int K, int N, int block_m, int block_n, int stages, int num_blocks, int num_sms,
+                        int32_t* out6);
+
+/* Tuning hook (tuners, tests): forces the number of CTAs per cluster along K for small batches; 0 = automatic
+ * choice (the default), otherwise 1, 2, 4 or 8.  Process-wide.  No counterpart in the reference. */
+int alpha_moe_b200_set_ksplit(int ksplit);
 
 const char* alpha_moe_b200_last_error(void);
 const char* alpha_moe_b200_version(void);

@@ -189,11 +189,18 @@ def test_torch_operator_path_and_errors():
             d["topk_weights"], out.float(), 2, 16, 32, 8, 3, 1.0)
 
 
+@pytest.fixture
+def ksplit_override():
+    from alpha_moe_b200 import capi
+    yield capi.set_ksplit
+    capi.set_ksplit(0)
+
+
 @pytest.mark.parametrize("ks", [1, 2, 4, 8])
-def test_k_split_over_a_cluster_small_batches(ks, monkeypatch):
+def test_k_split_over_a_cluster_small_batches(ks, ksplit_override):
     """Small batches: each (block, slice) is shared by a cluster of ks CTAs that split K and exchange partial
-    sums through distributed shared memory.  ALPHA_MOE_KSPLIT overrides the automatic choice."""
-    monkeypatch.setenv("ALPHA_MOE_KSPLIT", str(ks))
+    sums through distributed shared memory.  alpha_moe_b200_set_ksplit overrides the automatic choice."""
+    ksplit_override(ks)
     w = test_deepseek_shard_shape_small_expert_count.weights
     for m, top_k in ((1, 5), (3, 5), (7, 3)):
         case = orc.make_case(16, 7168, 256, m, top_k, seed=50 + m, shared=True, scaling=2.5, weights=w)

@@ -104,15 +104,43 @@ def test_fused_experts_entry_rejects_bad_arguments_without_a_gpu():
 
 
 def test_plan_fits_shared_memory_for_every_knob():
+    """alpha_moe_b200_plan runs the launcher's own planning code: ring depth, tile, shared memory, slices per CTA,
+    K-split and kernel for every knob tuple, slice count and batch regime."""
     from alpha_moe_b200 import capi
     for k in (128, 2048, 4096, 7168):
-        for bm in range(8, 129, 8):
-            for st in range(1, 6):
-                for bn in (32, 64):
-                    depth, bmp, smem, spc = capi.plan(k, bm, st, bn)
-                    assert 1 <= depth <= st and bmp >= bm and bmp in (16, 32, 64, 128)
-                    assert smem <= 232448 and spc == (2 if bn == 64 else 1)
+        for n in (256, 512, 768, 4096):
+            for bm in range(8, 129, 8):
+                for st in range(1, 6):
+                    for bn in (32, 64):
+                        for nblocks in (9, 600):
+                            depth, bmp, smem, spc, ks, kern = capi.plan(k, bm, st, bn, N=n, num_blocks=nblocks)
+                            assert 1 <= depth <= st and bmp >= bm and bmp in (16, 32, 64, 128)
+                            assert smem <= 232448
+                            assert spc == (2 if bn == 64 and (n // 256) % 2 == 0 else 1)
+                            assert kern == (0 if bm <= 64 else 1)
+                            assert ks in (1, 2, 4) and (ks == 1 or (bm <= 32 and spc == 1 and nblocks == 9))
     assert capi.plan(7168, 16, 5)[0] == 5
+    # a handful of live blocks at the DeepSeek shard shape: clusters of four CTAs along K
+    assert capi.plan(7168, 16, 5, 32, N=512, num_blocks=9)[4] == 4
+    assert capi.plan(7168, 16, 5, 32, N=512, num_blocks=40)[4] == 1
+    with pytest.raises(capi.AlphaMoeError):
+        capi.set_ksplit(3)
+
+
+def test_out_alignment_is_checked_per_kernel_before_anything_is_launched():
+    """block_m > 64 accumulates with 16-byte vector reductions: an `out` that is only 4-byte aligned must be
+    rejected with an argument error (it would fault on the device); block_m <= 64 accepts it.  The call with
+    block_m = 16 gets past the argument checks and fails later (no CUDA device / fake pointers), not with the alignment message."""
+    from alpha_moe_b200 import capi
+    p = 0x10000
+    args = dict(x=p, x_scale=p, w=p, w_scale=p, w2=p, w2_scale=p, out=p + 4, sid=p, eid=p, npp=p, tw=p, top_k=2, M=4,
+                K=512, N=256, E=8, sorted_num=128, block_m=128, block_n=64, warp_n=4, stages=3, scaling=1.0)
+    with pytest.raises(capi.AlphaMoeError, match="16-byte aligned"):
+        capi.fused_moe_w8a8_up_down(*args.values())
+    args["out"] = p + 2
+    args["block_m"] = 16
+    with pytest.raises(capi.AlphaMoeError, match="4-byte aligned"):
+        capi.fused_moe_w8a8_up_down(*args.values())
 
 
 def test_torch_operator_schema_is_the_reference_schema():
@@ -140,3 +168,34 @@ def test_no_product_module_imports_the_oracle():
             if fn.endswith((".py", ".cu", ".cuh", ".cpp", ".h")):
                 text = open(os.path.join(dirpath, fn)).read()
                 assert "oracle" not in text.replace("# oracle", ""), f"{fn} mentions the oracle"
+
+
+def test_layer_entry_checks_shapes_strides_and_dtypes_before_taking_pointers():
+    """alpha_moe_b200.layer.fused_experts_impl hands raw addresses to the C ABI, so it makes the operator's
+    tensor checks itself: a mismatched shard, a non-contiguous view or a wrong dtype raises, nothing is launched."""
+    from alpha_moe_b200.layer import _check_layer_arguments, fused_experts_impl
+    e, n, k, m, top_k = 4, 256, 256, 3, 2
+    good = dict(
+        hidden_states=torch.zeros(m, k, dtype=torch.bfloat16),
+        w1=torch.zeros(e, n, k, dtype=torch.float8_e4m3fn), w1_scale=torch.zeros(e, n // 128, k // 128),
+        w2=torch.zeros(e, k, n // 2, dtype=torch.float8_e4m3fn), w2_scale=torch.zeros(e, k // 128, n // 256),
+        topk_weights=torch.zeros(m, top_k), topk_ids=torch.zeros(m, top_k, dtype=torch.int32))
+    _check_layer_arguments(**good)
+    bad = [
+        dict(hidden_states=torch.zeros(m, k)),                                              # dtype
+        dict(hidden_states=torch.zeros(m, 2 * k, dtype=torch.bfloat16)[:, ::2]),            # strided view
+        dict(w1=torch.zeros(e, n, k // 2, dtype=torch.float8_e4m3fn)),                      # K mismatch
+        dict(w1=torch.zeros(e, 2 * n, k, dtype=torch.float8_e4m3fn)[:, ::2]),               # non-contiguous shard
+        dict(w2=torch.zeros(e, k, n, dtype=torch.float8_e4m3fn)),                           # w2 != [E, K, N/2]
+        dict(w2=torch.zeros(e, k, n // 2, dtype=torch.uint8)),                              # dtype
+        dict(w1_scale=torch.zeros(e, n // 128, k // 128 + 1)),
+        dict(w2_scale=torch.zeros(e, k // 128, n // 256, dtype=torch.float64)),
+        dict(topk_ids=torch.zeros(m + 1, top_k, dtype=torch.int32)),
+        dict(topk_weights=torch.zeros(m, top_k + 1)),
+    ]
+    for change in bad:
+        with pytest.raises(RuntimeError):
+            _check_layer_arguments(**dict(good, **change))
+    with pytest.raises(RuntimeError, match="CUDA"):
+        fused_experts_impl(good["hidden_states"], good["w1"], good["w1_scale"], good["w2"], good["w2_scale"],
+                           good["topk_weights"], good["topk_ids"], config=dict(block_m=16, block_n=32, warp_n=8, stages=3))
