@@ -118,10 +118,33 @@ fused_moe_w8a8_up_down_sm100_kernel(const __grid_constant__ CUtensorMap tm_w,
     const int ngroups = (p.N >> 8) / SPC;
     const int mblock = unit / ngroups;
     const int slice0 = (unit - mblock * ngroups) * SPC;
-    const int npad = min(p.num_tokens_post_padded[0], p.sorted_num);
-    if (mblock * p.block_m >= npad) return;          // block beyond the padded schedule (reference :678)
-    const int expert = p.expert_ids[mblock];
-    if (expert < 0 || expert >= p.E) return;         // (a whole cluster leaves together: same block)
+    const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
+    // Everything whose address is known at entry is requested here, before the early exit and the set-up work
+    // (barriers, TMEM, cluster sync), whose time then overlaps the latency of these loads: the schedule's length,
+    // this block's expert (in bounds: the launcher starts no more blocks than expert_ids has entries) and the
+    // sorted ids this thread will need - a gather thread those of its rows, an epilogue thread that of one token
+    // column.  What depends on them (token rows, token scales, routing weights, block scales) follows after set-up.
+    constexpr int PRE = BMP / 8;
+    int pid_pre[PRE];
+    int expert;
+    {
+        const int npad_raw = ld_global_nc_s32(p.num_tokens_post_padded);
+        const int expert_raw = ld_global_nc_s32(p.expert_ids + mblock);
+        const bool gather_role = warp >= 4 * EW && warp < 4 * EW + 2;
+        const int first = gather_role ? ((threadIdx.x - 4 * EW * 32) >> 3) : (threadIdx.x % BMP);
+#pragma unroll
+        for (int i = 0; i < PRE; ++i) {
+            const int row = first + 8 * i;
+            const int idx = mblock * p.block_m + row;
+            pid_pre[i] = -1;
+            if ((gather_role || i == 0) && warp < 4 * EW + 2 && row < p.block_m && idx < p.sorted_num)
+                pid_pre[i] = ld_global_nc_s32(p.sorted_token_ids + idx);
+        }
+        const int npad = min(npad_raw, p.sorted_num);
+        if (mblock * p.block_m >= npad) return;          // block beyond the padded schedule (reference :678)
+        if (expert_raw < 0 || expert_raw >= p.E) return; // (a whole cluster leaves together: same block)
+        expert = expert_raw;
+    }
 
     const int KC = p.K >> 7;                         // 128-deep K chunks of the up-projection
     const int kc_begin = crank * KC / ks, kc_end = (crank + 1) * KC / ks;       // this CTA's K chunks
@@ -131,7 +154,6 @@ fused_moe_w8a8_up_down_sm100_kernel(const __grid_constant__ CUtensorMap tm_w,
     const int ND = (crank + 1) * nd_all / ks - jt_begin;                        // down-projection iterations
     const int NIT = UPI + ND;
     const int S = p.stages;
-    const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
     if (threadIdx.x == 0) AMOE_STAMP(6, 0);
 #ifdef AMOE_TRACE
     if (p.trace && threadIdx.x == 0) {
@@ -275,16 +297,13 @@ fused_moe_w8a8_up_down_sm100_kernel(const __grid_constant__ CUtensorMap tm_w,
         const bool tma_thread = gtid == 0;
         const int row0 = gtid >> 3, ch = gtid & 7;
         uint32_t src16[PIECES];                     // (row * K) / 16, or 0xFFFFFFFF for a padding row
+        static_assert(PIECES == PRE, "one preloaded id per gathered row");
 #pragma unroll
         for (int i = 0; i < PIECES; ++i) {
-            const int row = row0 + 8 * i;
-            const int idx = mblock * p.block_m + row;
+            const int pid = pid_pre[i];             // requested at kernel entry; -1 for rows past the block
             src16[i] = 0xFFFFFFFFu;
-            if (row < p.block_m && idx < p.sorted_num) {
-                const int pid = p.sorted_token_ids[idx];
-                if (pid >= 0 && pid < p.M * p.top_k)
-                    src16[i] = static_cast<uint32_t>((static_cast<size_t>(pid / p.top_k) * p.K) >> 4);
-            }
+            if (pid >= 0 && pid < p.M * p.top_k)
+                src16[i] = static_cast<uint32_t>((static_cast<size_t>(pid / p.top_k) * p.K) >> 4);
         }
         if (tma_thread) {
             prefetch_tmap(&tm_w);
@@ -349,19 +368,20 @@ fused_moe_w8a8_up_down_sm100_kernel(const __grid_constant__ CUtensorMap tm_w,
         const int r = q * 32 + lane;         // weight row inside the tile = TMEM lane
         const int etid = threadIdx.x;
         const int mtk = p.M * p.top_k;
-        for (int j = etid; j < BMP; j += EPI_THREADS) {
-            int row = p.M;
-            float tw = 0.f;
-            const int idx = mblock * p.block_m + j;
-            if (j < p.block_m && idx < p.sorted_num) {
-                const int pid = p.sorted_token_ids[idx];
-                if (pid >= 0 && pid < mtk) {
-                    row = pid / p.top_k;             // reference :757
-                    tw = p.topk_weights[pid];        // reference :761
-                }
+        // One token column per thread (column etid % BMP; its sorted id was requested at kernel entry): its row, its
+        // routing weight, and its token scales for the K chunks etid / BMP, + EPI_THREADS / BMP, ...  No thread needs
+        // another thread's result here, so one barrier publishes everything.
+        {
+            const int j = etid % BMP;
+            const int pid = pid_pre[0];
+            const bool live = pid >= 0 && pid < mtk;
+            const int row = live ? pid / p.top_k : p.M;          // reference :757
+            if (etid < BMP) {
+                tokrow[j] = row;
+                topkw[j] = live ? p.topk_weights[pid] : 0.f;     // reference :761
             }
-            tokrow[j] = row;
-            topkw[j] = tw;
+            const float* xs_row = p.x_scale + static_cast<size_t>(live ? row : 0) * KC;
+            for (int c = etid / BMP; c < KC; c += EPI_THREADS / BMP) xs[c * BMP + j] = live ? xs_row[c] : 0.f;
         }
         {
             const int nsr = p.N >> 7;                         // scale rows per expert in w_scale
@@ -375,17 +395,11 @@ fused_moe_w8a8_up_down_sm100_kernel(const __grid_constant__ CUtensorMap tm_w,
             }
         }
         named_bar_sync(1, EPI_THREADS);
-        for (int i = etid; i < BMP * KC; i += EPI_THREADS) {
-            const int j = i / KC, c = i - j * KC;
-            const int row = tokrow[j];
-            xs[c * BMP + j] = row < p.M ? p.x_scale[static_cast<size_t>(row) * KC + c] : 0.f;
-        }
         int nhi = 0;
         for (int j = 0; j < BMP; ++j)
             if (tokrow[j] < p.M) nhi = j + 1;
         const int my_ncols = min(max(nhi - hh * NC, 0), NC);
         const bool few = nhi <= 2 && NEPI_WG == 1;   // at most two live columns in the whole block (CTA-uniform)
-        named_bar_sync(1, EPI_THREADS);
         if (etid == 0) AMOE_STAMP(6, 3);
 
         float accg[NC], accu[NC];
@@ -462,15 +476,30 @@ fused_moe_w8a8_up_down_sm100_kernel(const __grid_constant__ CUtensorMap tm_w,
                     if (!mbar_wait_cluster(peer_ready, 0, abort_flag, p.status, 43, it)) ok = false;
                     // After a wait that ran out, a peer may have left already: no peer's shared memory is read from
                     // here on (this CTA is unwinding; its sums are not used any more).
-                    const uint32_t my_part = smem_u32(part);
+                    // A load from a peer's shared memory takes several hundred cycles, and a thread that adds each value
+                    // as it arrives waits that long per value: all loads of a column (2 x up to 8 peers) are issued
+                    // before the first addition.
+                    uint32_t peer_part[8];
+#pragma unroll
+                    for (int peer = 0; peer < 8; ++peer) peer_part[peer] = mapa_shared(smem_u32(part), peer < ks ? peer : 0);
 #pragma unroll
                     for (int j = 0; j < NC; ++j) {
                         if (j < my_ncols && ok) {
+                            float vg[8], vu[8];
+#pragma unroll
+                            for (int peer = 0; peer < 8; ++peer) {
+                                vg[peer] = 0.f;
+                                vu[peer] = 0.f;
+                                if (peer < ks) {
+                                    vg[peer] = ld_dsmem_f32(peer_part[peer] + ((hh * NC + j) * 128 + r) * 4);
+                                    vu[peer] = ld_dsmem_f32(peer_part[peer] + ((BMP + hh * NC + j) * 128 + r) * 4);
+                                }
+                            }
                             float g = 0.f, u = 0.f;
-                            for (int peer = 0; peer < ks; ++peer) {
-                                const uint32_t base = mapa_shared(my_part, peer);
-                                g += ld_dsmem_f32(base + ((hh * NC + j) * 128 + r) * 4);
-                                u += ld_dsmem_f32(base + ((BMP + hh * NC + j) * 128 + r) * 4);
+#pragma unroll
+                            for (int peer = 0; peer < 8; ++peer) {      // in peer order: every CTA of the cluster gets the same sums
+                                g += vg[peer];
+                                u += vu[peer];
                             }
                             accg[j] = g;
                             accu[j] = u;

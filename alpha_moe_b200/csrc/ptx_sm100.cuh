@@ -315,6 +315,13 @@ template <int N>
 __device__ __forceinline__ void setmaxnreg_dec() {
     asm volatile("setmaxnreg.dec.sync.aligned.u32 %0;" ::"n"(N));
 }
+// Read-only global load that the compiler keeps where it is written (used to request small schedule words
+// at kernel entry, ahead of the set-up work whose latency they then overlap).
+__device__ __forceinline__ int ld_global_nc_s32(const int* p) {
+    int v;
+    asm volatile("ld.global.nc.s32 %0, [%1];" : "=r"(v) : "l"(p));
+    return v;
+}
 __device__ __forceinline__ float bf16_round(float v) { return __bfloat162float(__float2bfloat16_rn(v)); }
 
 }  // namespace amoe
