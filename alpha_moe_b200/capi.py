@@ -23,6 +23,10 @@ _vp, _i, _f = ctypes.c_void_p, ctypes.c_int, ctypes.c_float
 
 lib.alpha_moe_b200_fused_moe_w8a8_up_down.restype = _i
 lib.alpha_moe_b200_fused_moe_w8a8_up_down.argtypes = [_vp] * 11 + [_i] * 10 + [_f, _vp]
+lib.alpha_moe_b200_fused_moe_w8a8_up_down_tp.restype = _i
+lib.alpha_moe_b200_fused_moe_w8a8_up_down_tp.argtypes = [_vp] * 6 + [ctypes.POINTER(_vp), _i, _i] + [_vp] * 4 + [_i] * 10 + [_f, _vp]
+lib.alpha_moe_b200_tp_barrier.restype = _i
+lib.alpha_moe_b200_tp_barrier.argtypes = [ctypes.POINTER(_vp), _i, _i, _i, _vp]
 lib.alpha_moe_b200_read_status.restype = _i
 lib.alpha_moe_b200_read_status.argtypes = [ctypes.POINTER(ctypes.c_int32), _i]
 lib.alpha_moe_b200_plan.restype = _i
@@ -39,6 +43,8 @@ lib.alpha_moe_b200_per_token_group_quant_fp8.restype = _i
 lib.alpha_moe_b200_per_token_group_quant_fp8.argtypes = [_vp, _vp, _vp, _i, _i, _i, _vp]
 lib.alpha_moe_b200_fused_experts.argtypes = [_vp] * 9 + [_i] * 5 + [_vp] * 4 + [_i] * 4 + [_f, _vp]
 lib.alpha_moe_b200_fused_experts.restype = _i
+lib.alpha_moe_b200_selftest_wait_timeout.restype = _i
+lib.alpha_moe_b200_selftest_wait_timeout.argtypes = [_i, _i, _i, _vp, _vp]
 lib.alpha_moe_b200_last_error.restype = ctypes.c_char_p
 lib.alpha_moe_b200_version.restype = ctypes.c_char_p
 
@@ -64,6 +70,24 @@ def fused_moe_w8a8_up_down(x, x_scale, w, w_scale, w2, w2_scale, out, sorted_tok
         x, x_scale, w, w_scale, w2, w2_scale, out, sorted_token_ids, expert_ids,
         num_tokens_post_padded, topk_weights, top_k, M, K, N, num_experts, sorted_num,
         block_m, block_n, warp_n, stages, scaling_factor, stream))
+
+
+def fused_moe_w8a8_up_down_tp(x, x_scale, w, w_scale, w2, w2_scale, outs, tp_rank, sorted_token_ids, expert_ids,
+                              num_tokens_post_padded, topk_weights, top_k, M, K, N, num_experts, sorted_num,
+                              block_m, block_n, warp_n, stages, scaling_factor, stream=0) -> None:
+    """Raw call of the tensor-parallel form: `outs` = device addresses of every rank's output buffer as seen from this
+    GPU (outs[tp_rank] is this rank's own); the other tensor arguments are device addresses (ints)."""
+    arr = (_vp * len(outs))(*outs)
+    _check(lib.alpha_moe_b200_fused_moe_w8a8_up_down_tp(
+        x, x_scale, w, w_scale, w2, w2_scale, arr, len(outs), tp_rank, sorted_token_ids, expert_ids,
+        num_tokens_post_padded, topk_weights, top_k, M, K, N, num_experts, sorted_num,
+        block_m, block_n, warp_n, stages, scaling_factor, stream))
+
+
+def tp_barrier(flags, tp_rank, timeout_ms=1000, stream=0) -> None:
+    """Enqueues the cross-GPU barrier; `flags` = device addresses of every rank's flag array (9 uint32 each)."""
+    arr = (_vp * len(flags))(*flags)
+    _check(lib.alpha_moe_b200_tp_barrier(arr, len(flags), tp_rank, timeout_ms, stream))
 
 
 def moe_align_block_size(topk_ids, numel, num_experts, block_m, sorted_token_ids, expert_ids,
@@ -97,6 +121,11 @@ def fused_experts(hidden_states, x_fp8, x_scale, w, w_scale, w2, w2_scale, topk_
                                             topk_weights, top_k, M, K, N, num_experts, sorted_token_ids, expert_ids,
                                             num_tokens_post_padded, align_workspace, block_m, block_n, warp_n, stages,
                                             scaling_factor, stream))
+
+
+def selftest_wait_timeout(limit_cycles: int, where: int, iter_: int, result2, stream=0) -> None:
+    """Launches the bounded-wait self-test; result2 = device address of two int32 (what the two waits returned)."""
+    _check(lib.alpha_moe_b200_selftest_wait_timeout(limit_cycles, where, iter_, result2, stream))
 
 
 def read_status(reset: bool = False):

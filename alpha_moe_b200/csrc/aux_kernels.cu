@@ -4,10 +4,13 @@
 //   * per-token-group fp8 quantisation of the activations (group = 128), optionally zeroing the
 //     bf16 source afterwards, which is what the call site does next (extra/sglang.patch:31).
 // Both are integer / byte work bound by memory traffic; no tensor cores involved.
+#include <cooperative_groups.h>
 #include <cuda_bf16.h>
 #include <cuda_fp8.h>
 #include <cuda_runtime.h>
 #include <stdint.h>
+
+#include <atomic>
 
 #include "../../include/alpha_moe_b200.h"
 #include "capi_internal.h"
@@ -29,12 +32,15 @@ using amoe_capi::fail;
 // multiple of `block`, the rest of the expert's last block holding the sentinel `numel`.
 //
 // Work is cut into chunks of kChunk consecutive assignments, one CTA each:
-//   pass 1  fill outputs with their defaults; per-chunk histogram -> hist[chunk][expert]
-//   pass 2  (one CTA) padded expert sizes, their exclusive scan, per-chunk start offsets,
-//           expert_ids per block, num_tokens_post_padded
-//   pass 3  stable scatter: warps walk their 128 assignments in order, ranking equal experts
-//           inside a warp round with match.any
-// When everything fits one chunk the three passes run inside one CTA of one launch.
+//   phase A  fill outputs with their defaults; per-chunk histogram -> hist[chunk][expert]
+//   phase B  every CTA derives, from the whole histogram table, the padded expert sizes, their exclusive scan and
+//            the first output slot of its own chunk's assignments of every expert; CTA 0 also writes expert_ids per
+//            block and num_tokens_post_padded
+//   phase C  stable scatter: warps walk their 128 assignments in order, ranking equal experts inside a warp round
+//            with match.any
+// One launch runs all three phases with a grid-wide barrier after phase A (a cooperative launch, used whenever all
+// chunks fit on the GPU at once); otherwise phase A and phases B + C are two launches of the same kernel.  When
+// everything fits one chunk the phases run inside one CTA of an ordinary launch.
 constexpr int kChunk = 1024;          // assignments per CTA (8 warps x 4 rounds x 32 lanes)
 constexpr int kAlignThreads = 256;
 constexpr int kMaxExperts = 1024;     // per-warp counters live in shared memory: 8 x E ints
@@ -80,69 +86,86 @@ __device__ __forceinline__ void scatter_chunk(const int32_t* ids, int numel, int
     }
 }
 
-__global__ void __launch_bounds__(kAlignThreads)
-moe_align_pass1_kernel(const int32_t* ids, int numel, int E, int block, int32_t* sorted, int sorted_len,
-                       int32_t* expert_ids, int n_blocks_max, int* hist /*[chunks][E]*/) {
-    __shared__ int cnt[8 * kMaxExperts];
-    const int gtid = blockIdx.x * kAlignThreads + threadIdx.x, gsz = gridDim.x * kAlignThreads;
-    for (int i = gtid; i < sorted_len; i += gsz) sorted[i] = numel;
-    for (int i = gtid; i < n_blocks_max; i += gsz) expert_ids[i] = 0;
-    count_chunk(ids, numel, blockIdx.x * kChunk, E, cnt);
-    for (int e = threadIdx.x; e < E; e += kAlignThreads) {
-        int s = 0;
-#pragma unroll
-        for (int w = 0; w < 8; ++w) s += cnt[w * E + e];
-        hist[blockIdx.x * E + e] = s;
-    }
-}
+constexpr int kPhaseA = 1, kPhaseBC = 2;
 
-// One CTA.  On exit hist[c][e] holds the first output slot of chunk c's assignments of expert e.
-__global__ void __launch_bounds__(1024)
-moe_align_pass2_kernel(int* hist, int chunks, int E, int block, int32_t* expert_ids, int32_t* num_post_pad) {
-    __shared__ int padded[kMaxExperts];
-    __shared__ int start[kMaxExperts + 1];
-    for (int e = threadIdx.x; e < E; e += blockDim.x) {
-        int tot = 0;
-        for (int c = 0; c < chunks; ++c) tot += hist[c * E + e];
-        padded[e] = (tot + block - 1) / block * block;
-    }
-    __syncthreads();
-    if (threadIdx.x == 0) {
-        int run = 0;
-        for (int e = 0; e < E; ++e) {
-            start[e] = run;
-            run += padded[e];
-        }
-        start[E] = run;
-        num_post_pad[0] = run;
-    }
-    __syncthreads();
-    for (int e = threadIdx.x; e < E; e += blockDim.x) {
-        int run = start[e];
-        for (int c = 0; c < chunks; ++c) {
-            const int n = hist[c * E + e];
-            hist[c * E + e] = run;
-            run += n;
-        }
-        for (int b = start[e] / block; b < start[e + 1] / block; ++b) expert_ids[b] = e;
-    }
-}
-
+// `phases` = kPhaseA, kPhaseBC or both; both only in a cooperative launch (grid-wide barrier in between).
 __global__ void __launch_bounds__(kAlignThreads)
-moe_align_pass3_kernel(const int32_t* ids, int numel, int E, const int* hist, int32_t* sorted) {
+moe_align_chunks_kernel(const int32_t* ids, int numel, int E, int block, int32_t* sorted, int sorted_len,
+                        int32_t* expert_ids, int n_blocks_max, int* hist /*[chunks][E]*/, int32_t* num_post_pad,
+                        int phases) {
     __shared__ int cnt[8 * kMaxExperts];
-    count_chunk(ids, numel, blockIdx.x * kChunk, E, cnt);
-    for (int e = threadIdx.x; e < E; e += kAlignThreads) {     // counts -> exclusive prefix over the 8 warps
-        int run = hist[blockIdx.x * E + e];
+    __shared__ int warp_tot[kAlignThreads / 32];
+    const int chunks = gridDim.x, chunk = blockIdx.x;
+    if (phases & kPhaseA) {
+        const int gtid = chunk * kAlignThreads + threadIdx.x, gsz = chunks * kAlignThreads;
+        for (int i = gtid; i < sorted_len; i += gsz) sorted[i] = numel;
+        for (int i = gtid; i < n_blocks_max; i += gsz) expert_ids[i] = 0;
+    }
+    count_chunk(ids, numel, chunk * kChunk, E, cnt);       // (needed by both phases: recounted in a second launch)
+    if (phases & kPhaseA) {
+        for (int e = threadIdx.x; e < E; e += kAlignThreads) {
+            int s = 0;
 #pragma unroll
-        for (int w = 0; w < 8; ++w) {
-            const int n = cnt[w * E + e];
-            cnt[w * E + e] = run;
-            run += n;
+            for (int w = 0; w < 8; ++w) s += cnt[w * E + e];
+            hist[chunk * E + e] = s;
         }
     }
+    if (!(phases & kPhaseBC)) return;
+    if (phases & kPhaseA) cooperative_groups::this_grid().sync();
+
+    // Phase B.  Thread t owns the experts [t * per, (t + 1) * per): their totals over all chunks, the part of it that
+    // precedes this chunk, and (after a scan over the padded totals) their first output slots.
+    const int per = (E + kAlignThreads - 1) / kAlignThreads;           // <= 4
+    int before[4], padded[4], mine = 0;
+#pragma unroll
+    for (int i = 0; i < 4; ++i) {
+        const int e = threadIdx.x * per + i;
+        before[i] = 0;
+        padded[i] = 0;
+        if (i < per && e < E) {
+            int tot = 0, bef = 0;
+#pragma unroll 8
+            for (int c = 0; c < chunks; ++c) {
+                const int v = hist[c * E + e];
+                tot += v;
+                bef += c < chunk ? v : 0;
+            }
+            before[i] = bef;
+            padded[i] = (tot + block - 1) / block * block;
+            mine += padded[i];
+        }
+    }
+    // exclusive scan of `mine` over the threads (warp shuffles, then the eight warp totals)
+    const int lane = threadIdx.x & 31, warp = threadIdx.x >> 5;
+    int incl = mine;
+#pragma unroll
+    for (int d = 1; d < 32; d <<= 1) {
+        const int v = __shfl_up_sync(0xFFFFFFFFu, incl, d);
+        if (lane >= d) incl += v;
+    }
+    if (lane == 31) warp_tot[warp] = incl;
     __syncthreads();
-    scatter_chunk(ids, numel, blockIdx.x * kChunk, E, cnt, sorted);
+    int run = incl - mine;
+    for (int w = 0; w < warp; ++w) run += warp_tot[w];
+#pragma unroll
+    for (int i = 0; i < 4; ++i) {
+        const int e = threadIdx.x * per + i;
+        if (i < per && e < E) {
+            if (chunk == 0)
+                for (int b = run / block; b < (run + padded[i]) / block; ++b) expert_ids[b] = e;
+            int slot = run + before[i];
+#pragma unroll
+            for (int w = 0; w < 8; ++w) {          // counts -> first slot of each warp's assignments of expert e
+                const int n = cnt[w * E + e];
+                cnt[w * E + e] = slot;
+                slot += n;
+            }
+            run += padded[i];
+        }
+    }
+    if (chunk == 0 && threadIdx.x == kAlignThreads - 1) num_post_pad[0] = run;     // the last thread's running end = total
+    __syncthreads();
+    scatter_chunk(ids, numel, chunk * kChunk, E, cnt, sorted);
 }
 
 // Everything in one CTA when there is a single chunk (numel <= kChunk: e.g. up to 113 tokens at top_k = 9).
@@ -280,12 +303,38 @@ int alpha_moe_b200_moe_align_block_size(const int32_t* topk_ids, int numel, int 
     }
     if (!workspace) return fail(ALPHA_MOE_E_ARG, "workspace is required for more than %d assignments", kChunk);
     int* hist = static_cast<int*>(workspace);
-    moe_align_pass1_kernel<<<chunks, kAlignThreads, 0, st>>>(topk_ids, numel, num_experts, block_m, sorted_token_ids,
-                                                            static_cast<int>(sorted_len), expert_ids, n_blocks_max, hist);
+    int sorted_len_i = static_cast<int>(sorted_len);
+    int n_blocks_max_v = n_blocks_max, numel_v = numel, e_v = num_experts, block_v = block_m;
+    // One cooperative launch when every chunk's CTA can be resident at once (the grid-wide barrier needs that);
+    // the capacity of a device is looked up once.
+    static std::atomic<int> capacity[64];
+    int dev = 0;
+    AUX_TRY(cudaGetDevice(&dev));
+    int cap = dev >= 0 && dev < 64 ? capacity[dev].load(std::memory_order_acquire) : 0;
+    if (cap == 0) {
+        int per_sm = 0, sms = 0, coop = 0;
+        AUX_TRY(cudaOccupancyMaxActiveBlocksPerMultiprocessor(&per_sm, moe_align_chunks_kernel, kAlignThreads, 0));
+        AUX_TRY(cudaDeviceGetAttribute(&sms, cudaDevAttrMultiProcessorCount, dev));
+        AUX_TRY(cudaDeviceGetAttribute(&coop, cudaDevAttrCooperativeLaunch, dev));
+        cap = coop ? per_sm * sms : -1;
+        if (cap == 0) cap = -1;
+        if (dev >= 0 && dev < 64) capacity[dev].store(cap, std::memory_order_release);
+    }
+    if (chunks <= cap) {
+        int phases = kPhaseA | kPhaseBC;
+        void* args[] = {&topk_ids, &numel_v, &e_v, &block_v, &sorted_token_ids, &sorted_len_i, &expert_ids,
+                        &n_blocks_max_v, &hist, &num_tokens_post_padded, &phases};
+        AUX_TRY(cudaLaunchCooperativeKernel(reinterpret_cast<void*>(moe_align_chunks_kernel), dim3(chunks),
+                                            dim3(kAlignThreads), args, 0, st));
+        return ALPHA_MOE_OK;
+    }
+    moe_align_chunks_kernel<<<chunks, kAlignThreads, 0, st>>>(topk_ids, numel, num_experts, block_m, sorted_token_ids,
+                                                             sorted_len_i, expert_ids, n_blocks_max, hist,
+                                                             num_tokens_post_padded, kPhaseA);
     AUX_TRY(cudaGetLastError());
-    moe_align_pass2_kernel<<<1, 1024, 0, st>>>(hist, chunks, num_experts, block_m, expert_ids, num_tokens_post_padded);
-    AUX_TRY(cudaGetLastError());
-    moe_align_pass3_kernel<<<chunks, kAlignThreads, 0, st>>>(topk_ids, numel, num_experts, hist, sorted_token_ids);
+    moe_align_chunks_kernel<<<chunks, kAlignThreads, 0, st>>>(topk_ids, numel, num_experts, block_m, sorted_token_ids,
+                                                             sorted_len_i, expert_ids, n_blocks_max, hist,
+                                                             num_tokens_post_padded, kPhaseBC);
     AUX_TRY(cudaGetLastError());
     return ALPHA_MOE_OK;
 }
@@ -312,7 +361,7 @@ int alpha_moe_b200_moe_align_block_size_noalloc(const int32_t* topk_ids, int num
         AUX_TRY(cudaGetSymbolAddress(reinterpret_cast<void**>(&ptr), g_align_scratch));
         scratch_of_device[dev] = ptr;
     }
-    // Nothing in the scratch has to start at zero: pass 1 overwrites every [chunk][expert] entry this call reads.
+    // Nothing in the scratch has to start at zero: phase A overwrites every [chunk][expert] entry this call reads.
     return alpha_moe_b200_moe_align_block_size(topk_ids, numel, num_experts, block_m, sorted_token_ids, expert_ids,
                                                num_tokens_post_padded, scratch_of_device[dev], stream);
 }

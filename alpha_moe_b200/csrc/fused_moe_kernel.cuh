@@ -33,12 +33,19 @@
 
 namespace amoe {
 
+constexpr int kMaxTpWorld = 8;       // ranks whose `out` buffers one launch can add into
+
 struct MoeParams {
     const uint8_t* x;          // fp8 e4m3 [M, K]
     const float* x_scale;      // [M, K/128]
     const float* w_scale;      // [E, N/128, K/128], gate/up rows interleaved by 1
     const float* w2_scale;     // [E, K/128, I/128]
     __nv_bfloat16* out;        // [M, K]
+    // Tensor parallelism with the exchange step fused into the epilogue (small batches): the other ranks' `out`
+    // buffers, mapped into this GPU's address space.  Every partial result is added into all tp_world buffers with
+    // plain reductions over NVLink (no multicast, no tensor map covers peer memory); 1 = no peers.
+    __nv_bfloat16* out_more[kMaxTpWorld - 1];
+    int tp_world;
     const int* sorted_token_ids;
     const int* expert_ids;
     const int* num_tokens_post_padded;
@@ -65,6 +72,12 @@ struct MoeParams {
 #endif
 
 constexpr int kTileBytes = 128 * 128;  // one 128-row x 128-byte operand tile
+
+// bf16x2 reduction of (lo, hi) into element offset `off` of this rank's `out` and of every peer's, if row < M.
+__device__ __forceinline__ void red_out_all_ranks(const MoeParams& p, size_t off, float lo, float hi, int row) {
+    red_add_bf16x2_if(p.out + off, lo, hi, row, p.M);
+    for (int pr = 0; pr + 1 < p.tp_world; ++pr) red_add_bf16x2_if(p.out_more[pr] + off, lo, hi, row, p.M);
+}
 
 struct SmemPlan {
     uint32_t stage_bytes, hq, xs, swg, swu, sw2, tokrow, topkw, tokscale, amax, part, bars, misc, total;
@@ -616,7 +629,7 @@ fused_moe_w8a8_up_down_sm100_kernel(const __grid_constant__ CUtensorMap tm_w,
                     if (tt == 0 || two) {
                         const int tile = 2 * jt + tt;
                         const float s2 = sw2[tile];
-                        __nv_bfloat16* obase = p.out + tile * 128 + (r & ~1);
+                        const size_t obase = static_cast<size_t>(tile) * 128 + (r & ~1);
                         // Straight-line over each live 16-column group (padding columns carry row == M and are
                         // masked at the reduction): per-pair branches would serialise this single warp.
 #pragma unroll
@@ -640,7 +653,7 @@ fused_moe_w8a8_up_down_sm100_kernel(const __grid_constant__ CUtensorMap tm_w,
                                     const float lo = odd ? recv : a;
                                     const float hi = odd ? bb : recv;
                                     const int row = odd ? r1 : r0;
-                                    red_add_bf16x2_if(obase + static_cast<size_t>(row) * p.K, lo, hi, row, p.M);
+                                    red_out_all_ranks(p, obase + static_cast<size_t>(row) * p.K, lo, hi, row);
                                 }
                             }
                         }
@@ -650,7 +663,7 @@ fused_moe_w8a8_up_down_sm100_kernel(const __grid_constant__ CUtensorMap tm_w,
                 // v0 / v1 = partial sums of hidden tile jt over slice 0 / slice 1: each has its own block scale
                 // and its own per-token quantisation scale, so they are combined here, then reduced once
                 const float s2a = sw2[jt], s2b = sw2[KC + jt];
-                __nv_bfloat16* obase = p.out + jt * 128 + (r & ~1);
+                const size_t obase = static_cast<size_t>(jt) * 128 + (r & ~1);
 #pragma unroll
                 for (int c0 = 0; c0 < NC; c0 += 16) {
                     if (c0 < my_ncols) {
@@ -668,7 +681,7 @@ fused_moe_w8a8_up_down_sm100_kernel(const __grid_constant__ CUtensorMap tm_w,
                             const float lo = odd ? recv : a;
                             const float hi = odd ? bb : recv;
                             const int row = odd ? rr.y : rr.x;
-                            red_add_bf16x2_if(obase + static_cast<size_t>(row) * p.K, lo, hi, row, p.M);
+                            red_out_all_ranks(p, obase + static_cast<size_t>(row) * p.K, lo, hi, row);
                         }
                     }
                 }

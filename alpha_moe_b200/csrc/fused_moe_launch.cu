@@ -216,6 +216,27 @@ int device_facts(int dev, DeviceFacts* out) {
     return ALPHA_MOE_OK;
 }
 
+// Self-test of the bounded wait: warp 0 waits on an mbarrier that nothing ever arrives on, with a limit given by the
+// caller; warp 1 waits on a second such barrier with the product's (one second) limit and must be released by the
+// CTA's abort flag when warp 0 gives up.  result[0] / result[1] = what the two waits returned (1 = barrier completed).
+__global__ void wait_selftest_kernel(amoe::KernelStatus* status, int* result, long long limit_cycles, int where, int iter) {
+    __shared__ uint64_t bars[2];
+    __shared__ int abort_flag;
+    if (threadIdx.x == 0) {
+        amoe::mbar_init(&bars[0], 1);
+        amoe::mbar_init(&bars[1], 1);
+        abort_flag = 0;
+        amoe::fence_mbar_init();
+    }
+    __syncthreads();
+    const int warp = threadIdx.x >> 5;
+    if ((threadIdx.x & 31) == 0) {
+        const bool done = warp == 0 ? amoe::mbar_wait_limit(&bars[0], 0, &abort_flag, status, where, iter, limit_cycles)
+                                    : amoe::mbar_wait(&bars[1], 0, &abort_flag, status, where + 1, iter);
+        result[warp] = done ? 1 : 0;
+    }
+}
+
 std::atomic<int> g_ksplit_override{0};     // 0 = automatic; set through alpha_moe_b200_set_ksplit (tuners, tests)
 
 // Clusters of 2 or 4 CTAs along K for small batches: as many as still fit one CTA per SM (narrow tile, one slice
@@ -230,19 +251,60 @@ int choose_ksplit(int block_m, int spc, long long nblocks, int N, int K, int sms
     return ksplit;
 }
 
-}  // namespace
+// Cross-GPU barrier of the fused tensor-parallel path.  flags[r] = rank r's flag array (kMaxTpWorld + 1 words of
+// symmetric memory, zero before the first use): word q = last epoch that rank q has announced to r, word kMaxTpWorld =
+// r's own epoch counter.  Thread t tells rank t "rank `rank` has reached epoch e" and waits (bounded) until rank t has
+// told this rank the same.  The stores are system-scope releases issued after the preceding kernel of the stream has
+// completed, so everything that kernel added into the peers' buffers is visible to whoever sees the flag.
+struct TpFlags {
+    uint32_t* of_rank[amoe::kMaxTpWorld];
+};
+__global__ void tp_barrier_kernel(TpFlags flags, int world, int rank, amoe::KernelStatus* status, long long limit_cycles) {
+    __shared__ uint32_t epoch;
+    uint32_t* mine = flags.of_rank[rank];
+    if (threadIdx.x == 0) {
+        epoch = mine[amoe::kMaxTpWorld] + 1;
+        mine[amoe::kMaxTpWorld] = epoch;
+    }
+    __syncthreads();
+    const int t = threadIdx.x;
+    if (t >= world) return;
+    const uint32_t e = epoch;
+    __threadfence_system();
+    asm volatile("st.release.sys.global.u32 [%0], %1;" ::"l"(flags.of_rank[t] + rank), "r"(e) : "memory");
+    const long long t0 = clock64();
+    for (;;) {
+        uint32_t seen;
+        asm volatile("ld.acquire.sys.global.u32 %0, [%1];" : "=r"(seen) : "l"(mine + t) : "memory");
+        if (static_cast<int32_t>(seen - e) >= 0) return;
+        if (clock64() - t0 > limit_cycles) {
+            if (atomicCAS(&status->code, amoe::ST_OK, amoe::ST_WAIT_TIMEOUT) == amoe::ST_OK) {
+                status->block = rank;
+                status->where = 90 + t;          // 90 + the rank that did not arrive
+                status->iter = static_cast<int>(e);
+            }
+            return;
+        }
+    }
+}
 
-extern "C" {
-
-int alpha_moe_b200_fused_moe_w8a8_up_down(const void* x, const float* x_scale, const void* w, const float* w_scale,
-                                          const void* w2, const float* w2_scale, void* out,
-                                          const int32_t* sorted_token_ids, const int32_t* expert_ids,
-                                          const int32_t* num_tokens_post_padded, const float* topk_weights, int top_k,
-                                          int M, int K, int N, int num_experts, int sorted_num, int block_m,
-                                          int block_n, int warp_n, int stages, float scaling_factor, void* stream) {
-    if (!x || !x_scale || !w || !w_scale || !w2 || !w2_scale || !out || !sorted_token_ids || !expert_ids ||
+int launch_fused(const void* x, const float* x_scale, const void* w, const float* w_scale, const void* w2,
+                 const float* w2_scale, void* const* outs, int tp_world, int tp_rank, const int32_t* sorted_token_ids,
+                 const int32_t* expert_ids, const int32_t* num_tokens_post_padded, const float* topk_weights, int top_k,
+                 int M, int K, int N, int num_experts, int sorted_num, int block_m, int block_n, int warp_n, int stages,
+                 float scaling_factor, void* stream) {
+    if (!x || !x_scale || !w || !w_scale || !w2 || !w2_scale || !outs || !sorted_token_ids || !expert_ids ||
         !num_tokens_post_padded || !topk_weights)
         return fail(ALPHA_MOE_E_ARG, "null pointer argument");
+    if (tp_world < 1 || tp_world > amoe::kMaxTpWorld || tp_rank < 0 || tp_rank >= tp_world)
+        return fail(ALPHA_MOE_E_ARG, "tp_world must be in 1..%d and 0 <= tp_rank < tp_world (got %d, %d)",
+                    amoe::kMaxTpWorld, tp_world, tp_rank);
+    for (int r = 0; r < tp_world; ++r)
+        if (!outs[r]) return fail(ALPHA_MOE_E_ARG, "null pointer argument (out of rank %d)", r);
+    if (tp_world > 1 && block_m > 64)
+        return fail(ALPHA_MOE_E_ARG, "the fused tensor-parallel exchange serves small batches: block_m <= 64 (got %d); "
+                                     "larger blocks run the plain operator followed by an all-reduce", block_m);
+    void* out = outs[tp_rank];
     if (M <= 0) return fail(ALPHA_MOE_E_ARG, "x must have at least one row (M=%d)", M);
     if (K <= 0 || K % 128 != 0) return fail(ALPHA_MOE_E_ARG, "K dimension must be a multiple of 128 (K=%d)", K);
     if (N <= 0 || N % 256 != 0) return fail(ALPHA_MOE_E_ARG, "N must be a multiple of 256 (N=%d)", N);
@@ -256,8 +318,9 @@ int alpha_moe_b200_fused_moe_w8a8_up_down(const void* x, const float* x_scale, c
     if ((reinterpret_cast<uintptr_t>(w) | reinterpret_cast<uintptr_t>(w2) | reinterpret_cast<uintptr_t>(x)) & 15)
         return fail(ALPHA_MOE_E_ARG, "x, w and w2 must be 16-byte aligned");
     // the token-major kernels accumulate with 16-byte vector reductions, the others with 4-byte ones
-    if (reinterpret_cast<uintptr_t>(out) & (token_major(block_m) ? 15 : 3))
-        return fail(ALPHA_MOE_E_ARG, "out must be %d-byte aligned for block_m=%d", token_major(block_m) ? 16 : 4, block_m);
+    for (int r = 0; r < tp_world; ++r)
+        if (reinterpret_cast<uintptr_t>(outs[r]) & (token_major(block_m) ? 15 : 3))
+            return fail(ALPHA_MOE_E_ARG, "out must be %d-byte aligned for block_m=%d", token_major(block_m) ? 16 : 4, block_m);
     if (static_cast<long long>(M) * top_k > 0x7FFFFFFFLL) return fail(ALPHA_MOE_E_ARG, "M*top_k overflows int32");
 
     int dev = 0;
@@ -284,6 +347,9 @@ int alpha_moe_b200_fused_moe_w8a8_up_down(const void* x, const float* x_scale, c
     p.w_scale = w_scale;
     p.w2_scale = w2_scale;
     p.out = static_cast<__nv_bfloat16*>(out);
+    p.tp_world = tp_world;
+    for (int i = 0; i < amoe::kMaxTpWorld - 1; ++i)       // the peers, starting behind this rank so that traffic spreads
+        p.out_more[i] = i + 1 < tp_world ? static_cast<__nv_bfloat16*>(outs[(tp_rank + 1 + i) % tp_world]) : nullptr;
     p.sorted_token_ids = sorted_token_ids;
     p.expert_ids = expert_ids;
     p.num_tokens_post_padded = num_tokens_post_padded;
@@ -328,6 +394,69 @@ int alpha_moe_b200_fused_moe_w8a8_up_down(const void* x, const float* x_scale, c
         default: return pair64 ? launch_variant<64, 2, 1>(maps, p, g, smem_bytes, dev, st)
                                : launch_variant<64, 2>(maps, p, g, smem_bytes, dev, st);
     }
+}
+
+}  // namespace
+
+extern "C" {
+
+int alpha_moe_b200_fused_moe_w8a8_up_down(const void* x, const float* x_scale, const void* w, const float* w_scale,
+                                          const void* w2, const float* w2_scale, void* out,
+                                          const int32_t* sorted_token_ids, const int32_t* expert_ids,
+                                          const int32_t* num_tokens_post_padded, const float* topk_weights, int top_k,
+                                          int M, int K, int N, int num_experts, int sorted_num, int block_m,
+                                          int block_n, int warp_n, int stages, float scaling_factor, void* stream) {
+    if (!out) return fail(ALPHA_MOE_E_ARG, "null pointer argument");
+    void* outs[1] = {out};
+    return launch_fused(x, x_scale, w, w_scale, w2, w2_scale, outs, 1, 0, sorted_token_ids, expert_ids,
+                        num_tokens_post_padded, topk_weights, top_k, M, K, N, num_experts, sorted_num, block_m, block_n,
+                        warp_n, stages, scaling_factor, stream);
+}
+
+int alpha_moe_b200_fused_moe_w8a8_up_down_tp(const void* x, const float* x_scale, const void* w, const float* w_scale,
+                                             const void* w2, const float* w2_scale, void* const* outs, int tp_world,
+                                             int tp_rank, const int32_t* sorted_token_ids, const int32_t* expert_ids,
+                                             const int32_t* num_tokens_post_padded, const float* topk_weights, int top_k,
+                                             int M, int K, int N, int num_experts, int sorted_num, int block_m,
+                                             int block_n, int warp_n, int stages, float scaling_factor, void* stream) {
+    return launch_fused(x, x_scale, w, w_scale, w2, w2_scale, outs, tp_world, tp_rank, sorted_token_ids, expert_ids,
+                        num_tokens_post_padded, topk_weights, top_k, M, K, N, num_experts, sorted_num, block_m, block_n,
+                        warp_n, stages, scaling_factor, stream);
+}
+
+int alpha_moe_b200_tp_barrier(void* const* flags, int tp_world, int tp_rank, int timeout_ms, void* stream) {
+    if (!flags) return fail(ALPHA_MOE_E_ARG, "flags is null");
+    if (tp_world < 1 || tp_world > amoe::kMaxTpWorld || tp_rank < 0 || tp_rank >= tp_world)
+        return fail(ALPHA_MOE_E_ARG, "tp_world must be in 1..%d and 0 <= tp_rank < tp_world (got %d, %d)",
+                    amoe::kMaxTpWorld, tp_world, tp_rank);
+    if (timeout_ms < 1 || timeout_ms > 2000) return fail(ALPHA_MOE_E_ARG, "timeout_ms must be in 1..2000, got %d", timeout_ms);
+    TpFlags f;
+    for (int r = 0; r < amoe::kMaxTpWorld; ++r) {
+        f.of_rank[r] = r < tp_world ? static_cast<uint32_t*>(flags[r]) : nullptr;
+        if (r < tp_world && (!flags[r] || (reinterpret_cast<uintptr_t>(flags[r]) & 3)))
+            return fail(ALPHA_MOE_E_ARG, "flag array of rank %d is null or misaligned", r);
+    }
+    int dev = 0;
+    CUDA_TRY(cudaGetDevice(&dev));
+    DeviceFacts facts;
+    if (int rc = device_facts(dev, &facts)) return rc;
+    const long long limit = static_cast<long long>(timeout_ms) * 2000000LL;      // about 2 GHz
+    tp_barrier_kernel<<<1, 32, 0, static_cast<cudaStream_t>(stream)>>>(f, tp_world, tp_rank, facts.status, limit);
+    CUDA_TRY(cudaGetLastError());
+    return ALPHA_MOE_OK;
+}
+
+int alpha_moe_b200_selftest_wait_timeout(int limit_cycles, int where, int iter, int32_t* result2, void* stream) {
+    if (!result2) return fail(ALPHA_MOE_E_ARG, "result2 is null");
+    if (limit_cycles < 1000 || limit_cycles > 200000000)
+        return fail(ALPHA_MOE_E_ARG, "limit_cycles must be in 1000..200000000 (about 0.1 s), got %d", limit_cycles);
+    int dev = 0;
+    CUDA_TRY(cudaGetDevice(&dev));
+    DeviceFacts facts;
+    if (int rc = device_facts(dev, &facts)) return rc;
+    wait_selftest_kernel<<<1, 64, 0, static_cast<cudaStream_t>(stream)>>>(facts.status, result2, limit_cycles, where, iter);
+    CUDA_TRY(cudaGetLastError());
+    return ALPHA_MOE_OK;
 }
 
 int alpha_moe_b200_set_ksplit(int ksplit) {

@@ -73,8 +73,8 @@ constexpr long long kWaitLimitCycles = 2000000000LL;
 // other waiter of that CTA returns false at its next poll, so the CTA unwinds as a whole.
 // (Kept inline: a device function call inside a role that has resized its register allotment with
 // setmaxnreg does not get through register allocation.)
-__device__ __forceinline__ bool mbar_wait(uint64_t* bar, uint32_t parity, volatile int* abort_flag,
-                                          KernelStatus* status, int where, int iter) {
+__device__ __forceinline__ bool mbar_wait_limit(uint64_t* bar, uint32_t parity, volatile int* abort_flag,
+                                                KernelStatus* status, int where, int iter, long long limit_cycles) {
     if (mbar_try_wait(bar, parity)) return true;
     const long long t0 = clock64();
     for (;;) {
@@ -82,7 +82,7 @@ __device__ __forceinline__ bool mbar_wait(uint64_t* bar, uint32_t parity, volati
         for (int i = 0; i < 32; ++i)
             if (mbar_try_wait(bar, parity)) return true;
         if (*abort_flag) return false;
-        if (clock64() - t0 > kWaitLimitCycles) {
+        if (clock64() - t0 > limit_cycles) {
             *abort_flag = 1;
             if (atomicCAS(&status->code, ST_OK, ST_WAIT_TIMEOUT) == ST_OK) {
                 status->block = blockIdx.x;
@@ -92,6 +92,10 @@ __device__ __forceinline__ bool mbar_wait(uint64_t* bar, uint32_t parity, volati
             return false;
         }
     }
+}
+__device__ __forceinline__ bool mbar_wait(uint64_t* bar, uint32_t parity, volatile int* abort_flag,
+                                          KernelStatus* status, int where, int iter) {
+    return mbar_wait_limit(bar, parity, abort_flag, status, where, iter, kWaitLimitCycles);
 }
 
 // --------------------------------------------------------------------------------------------- clusters / DSMEM

@@ -3,8 +3,9 @@ format ({"<M>": {"block_m", "block_n", "warp_n", "stages"}}) that `get_best_conf
 `ALPHA_MOE_CONFIG` consume.
 
 Counterpart of the reference's jit_moe.py:104-184 (brute force over the knob space per token count,
-arg-min per M).  Differences: timing uses CUDA events with the L2 flushed between calls instead of the
-Kineto profile (jit_moe.py:15-32); the schedule and the activation quantisation come from this
+arg-min per M).  Differences: timing uses CUDA events with the L2 flushed between calls by default
+(`--timing kineto` takes the reference's method instead: mean device time of the kernels whose name contains
+"moe" in a torch.profiler trace, jit_moe.py:15-32); the schedule and the activation quantisation come from this
 library's own kernels instead of SGLang's; by default only knob values that map to distinct kernel
 configurations are tried (`--full` sweeps all 160 combinations like the reference).
 
@@ -53,6 +54,35 @@ def time_call(fn, flush, iters: int, warmup: int = 2) -> float:
     return ts[len(ts) // 2] * 1e3   # median, microseconds
 
 
+def time_call_kineto(fn, flush, iters: int, kernel_name: str = "moe") -> float:
+    """The reference's timing method (jit_moe.py:15-32): one warm-up cycle and one recorded cycle of `iters` calls
+    under torch.profiler (CUDA activity), the L2 evicted before every call, mean device time of the kernels whose
+    name contains `kernel_name`; microseconds."""
+    from torch.profiler import ProfilerActivity, profile, schedule
+    with profile(activities=[ProfilerActivity.CUDA], schedule=schedule(wait=0, warmup=1, active=1, repeat=1)) as prof:
+        for _ in range(2):
+            for _ in range(iters):
+                flush.zero_()
+                fn()
+                torch.cuda.synchronize()
+            prof.step()
+    times = [e.device_time_total for e in prof.profiler.function_events if kernel_name in e.name]
+    if not times:
+        raise RuntimeError(f"no kernel with '{kernel_name}' in its name in the profile")
+    return sum(times) / len(times)
+
+
+def parse_knobs(items):
+    """'16,32,8,3' -> (16, 32, 8, 3) for every item."""
+    out = []
+    for it in items:
+        parts = tuple(int(v) for v in it.split(","))
+        if len(parts) != 4:
+            raise ValueError(f"a knob tuple is block_m,block_n,warp_n,stages - got '{it}'")
+        out.append(parts)
+    return out
+
+
 def main(argv=None):
     ap = argparse.ArgumentParser(description="B200 knob search for alpha_moe::fused_moe_w8a8_up_down")
     ap.add_argument("--E", type=int, default=256, help="routed experts (the shared expert is added on top)")
@@ -64,6 +94,9 @@ def main(argv=None):
     ap.add_argument("--routings", type=int, default=2, help="random routings averaged per token count")
     ap.add_argument("--iters", type=int, default=7)
     ap.add_argument("--full", action="store_true", help="sweep all 160 knob combinations")
+    ap.add_argument("--knobs", nargs="+", default=None, metavar="BM,BN,WN,ST", help="search these tuples only")
+    ap.add_argument("--timing", choices=["events", "kineto"], default="events",
+                    help="CUDA events (default) or the reference's torch.profiler method")
     ap.add_argument("--scaling-factor", type=float, default=2.5)
     ap.add_argument("--out-file", default=None)
     args = ap.parse_args(argv)
@@ -98,7 +131,7 @@ def main(argv=None):
                 wts = torch.cat([wts, torch.ones(m, 1, device=dev)], 1)
             routings.append((ids.contiguous(), wts.float().contiguous()))
         best, best_us = None, float("inf")
-        for bm, bn, wn, st in knob_space(args.full):
+        for bm, bn, wn, st in (parse_knobs(args.knobs) if args.knobs else knob_space(args.full)):
             if m < bm and bm != 16:          # same pruning as the reference sweep (jit_moe.py:153-154)
                 continue
             total = 0.0
@@ -108,10 +141,12 @@ def main(argv=None):
                 def call():
                     op(x, x_scale, w, w_scale, w2, w2_scale, sid, eid, npp, wts, out, top_k, bm, bn, wn, st,
                        args.scaling_factor)
-                total += time_call(call, flush, args.iters)
+                total += (time_call_kineto if args.timing == "kineto" else time_call)(call, flush, args.iters)
             us = total / len(routings)
             if us < best_us:
                 best, best_us = (bm, bn, wn, st), us
+        if best is None:
+            raise RuntimeError(f"no knob tuple is admissible for M={m}")
         table[str(m)] = {"block_m": best[0], "block_n": best[1], "warp_n": best[2], "stages": best[3]}
         report[m] = best_us
         print(f"M={m:5d}: best {best} {best_us:9.1f} us", flush=True)

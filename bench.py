@@ -8,7 +8,8 @@ Headline workload at every N: the DeepSeek-V3 TP8 shard per GPU (E=257 incl. the
 K=7168, I=256 per GPU, top_k=8+1, routed_scaling_factor=2.5), M=4096, i.e. N GPUs serve a layer whose
 intermediate size is 256*N ("weak" scaling; N=8 is the real DeepSeek-V3 layer, I=2048, TP8).
 Beside the headline the JSON line carries sub-records for the rest of the metric:
-  sweep    the headline shape over M = 1 ... 8192
+  sweep    the headline shape over M = 1 ... 8192 (at N > 1 and M <= 64 also with the exchange step fused into
+           the kernel instead of the all-reduce: us_step_fused_tp)
   qwen3    the Qwen3-Next TP2 shard (E=512, K=2048, I=256, top_k=10) over M      (1 GPU only)
   zipf     the headline shape at M=8192 with Zipf(1.2) routing                   (1 GPU only)
   tp_fixed the unsharded layer I=2048 split I/N per GPU ("strong" scaling) at M = 1, 64, 1024, 8192
@@ -465,6 +466,33 @@ def main():
         launches[0] += steps
         return tot / steps
 
+    fused_tp = {}
+
+    def time_fused_tp(wl, m, steps, warmup):
+        """Small batches on N > 1 ranks with the exchange step fused into the kernel: reductions into every rank's
+        peer-mapped `out`, clearing of the next buffer and this library's cross-GPU barrier; no collective call."""
+        from alpha_moe_b200.tp import PeerReducedLayer
+        sh = wl.shape
+        if "layer" not in fused_tp:
+            fused_tp["layer"] = PeerReducedLayer(64, sh.k)
+        lay = fused_tp["layer"]
+        inp, d, _, _, (bm, bn, wn, st) = prepare(wl, m)
+        tot = 0.0
+        for i in range(warmup + steps):
+            flush.fill_(i & 0xFF)
+            barrier()
+            e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+            e0.record()
+            lay.run(inp["x"], inp["x_scale"], wl.w, wl.w_scale, wl.w2, wl.w2_scale, d["sid"], d["eid"], d["npp"],
+                    d["topk_weights"], sh.top_k, bm, bn, wn, st, sh.scaling)
+            e1.record()
+            torch.cuda.synchronize()
+            if i >= warmup:
+                tot += e0.elapsed_time(e1)
+        launches[0] += 2 * steps
+        (ms,) = max_over_ranks(tot / steps)
+        return ms
+
     def time_layer(wl, m, steps, warmup):
         """The call-site sequence as one C-ABI call (alpha_moe_b200_fused_experts): bf16 activations and topk_ids in,
         layer output in the same buffer: group quantisation + clearing + block schedule + fused operator."""
@@ -678,6 +706,8 @@ def main():
             extra = {}
             if world == 1 and ms_ <= GRAPH_MAX_M:
                 extra["us_step_graph"] = round(time_graph_step(wl, ms_, 10) * 1e3, 1)
+            if world > 1 and ms_ <= 64 and sk[0] <= 64:
+                extra["us_step_fused_tp"] = round(time_fused_tp(wl, ms_, 10, 3) * 1e3, 1)
             sweep.append(sweep_record(sh, ms_, s_ms, k_ms, sinp, sk, extra))
         for ms_ in LAYER_MS:
             if world == 1:

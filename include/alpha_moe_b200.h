@@ -44,6 +44,32 @@ int alpha_moe_b200_fused_moe_w8a8_up_down(
     int num_experts, int sorted_num, int block_m, int block_n, int warp_n, int stages,
     float scaling_factor, void* stream);
 
+/* Tensor-parallel form of the operator with the exchange step fused into the kernel's epilogue, for small batches
+ * (block_m <= 64); no counterpart in the reference, whose caller all-reduces the partial outputs afterwards
+ * (extra/sglang.patch:38-41, README.md:1).  Arguments as above, except that `out` becomes `outs`: a HOST array of
+ * tp_world device pointers, outs[r] = rank r's [M,K] bf16 output buffer mapped into this GPU's address space
+ * (CUDA IPC / virtual-memory export, e.g. torch.distributed._symmetric_memory); outs[tp_rank] is this GPU's own.
+ * Every rank runs the call on its shard of the intermediate dimension with the same x / routing / schedule, and each
+ * partial result is added into all tp_world buffers with plain reductions over NVLink, so that after a cross-GPU
+ * barrier (alpha_moe_b200_tp_barrier) every rank holds the full layer output and no collective call is needed.
+ * All tp_world buffers must be zero before ANY rank starts: clear a buffer before the barrier of the previous step
+ * (use two buffers alternately).  tp_world <= 8.  The kernel itself waits for no other GPU. */
+int alpha_moe_b200_fused_moe_w8a8_up_down_tp(
+    const void* x, const float* x_scale, const void* w, const float* w_scale, const void* w2,
+    const float* w2_scale, void* const* outs, int tp_world, int tp_rank, const int32_t* sorted_token_ids,
+    const int32_t* expert_ids, const int32_t* num_tokens_post_padded, const float* topk_weights, int top_k, int M,
+    int K, int N, int num_experts, int sorted_num, int block_m, int block_n, int warp_n, int stages,
+    float scaling_factor, void* stream);
+
+/* Barrier over the tp_world GPUs of the fused tensor-parallel path, enqueued on `stream` (no counterpart in the
+ * reference).  flags: HOST array of tp_world device pointers, flags[r] = rank r's flag array of 9 uint32 in memory
+ * that every rank can write (symmetric memory), all zero before the first barrier.  Work enqueued on this stream
+ * before the barrier on every rank (the reductions of alpha_moe_b200_fused_moe_w8a8_up_down_tp, the clearing of the
+ * next buffer) is complete and visible on every rank once the barrier has passed there.  The wait is bounded: after
+ * timeout_ms (1..2000) the kernel records {code 1, this rank, 90 + the rank that did not arrive, epoch} in the status
+ * word and returns; read it with alpha_moe_b200_read_status.  Nothing traps. */
+int alpha_moe_b200_tp_barrier(void* const* flags, int tp_world, int tp_rank, int timeout_ms, void* stream);
+
 /* Replaces the external moe_align_block_size the reference calls before the operator
  * (jit_moe.py:158, extra/sglang.patch:33-35).  topk_ids [numel] i32 (the flattened [M,top_k] expert
  * ids; ids outside [0,num_experts) are ignored).  Outputs: sorted_token_ids
@@ -98,6 +124,16 @@ int alpha_moe_b200_fused_experts(void* hidden_states, void* x_fp8, float* x_scal
 /* Reads (and optionally clears) the status word of the current device: out4 = {code, block, where, iter};
  * code 0 means no kernel wait has ever run out.  Synchronises the device. */
 int alpha_moe_b200_read_status(int32_t* out4, int reset);
+
+/* Self-test of the bounded device waits (no counterpart in the reference, whose wait at
+ * csrc/kernels/fused_moe_w8a8/fused_moe_w8a8_up_down_acc.cu:563-575 spins without limit).  Launches one small CTA
+ * in which one warp waits, with a limit of `limit_cycles` SM clocks, on an mbarrier that nothing ever arrives on,
+ * and a second warp waits on another such barrier with the product kernels' own limit.  The first wait runs out,
+ * records {code = 1 (wait ran out), block = 0, where, iter} in the device status word and raises the CTA's abort flag,
+ * which releases the second waiter; the kernel then returns normally (nothing traps or faults, the context stays
+ * usable).  result2 (device, 2 x int32) receives what the two waits returned: 0 = gave up.  Read the status word
+ * with alpha_moe_b200_read_status afterwards (and clear it).  limit_cycles in 1000..200000000. */
+int alpha_moe_b200_selftest_wait_timeout(int limit_cycles, int where, int iter, int32_t* result2, void* stream);
 
 /* What the launcher uses for a problem and a knob tuple; for tuners and tests.  It runs the launcher's own
  * planning code.  num_blocks = live upper bound of schedule blocks, min(ceil(sorted_num / block_m), M * top_k);

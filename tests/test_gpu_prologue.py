@@ -23,6 +23,21 @@ def test_moe_align_block_size_matches_oracle_exactly(m, e, k, block):
         assert torch.equal(a.cpu(), b), name
 
 
+def test_moe_align_more_chunks_than_fit_on_the_gpu_and_many_experts():
+    """About a million assignments are more 1024-assignment chunks than can be resident at once, so the schedule is
+    built by two launches instead of one cooperative launch; 1000 experts exercises several experts per thread in
+    the offset computation.  Both bit-exact against the CPU restatement."""
+    from alpha_moe_b200.prologue import moe_align_block_size
+    g = torch.Generator().manual_seed(11)
+    for m, e, k, block in ((130000, 257, 9, 128), (3000, 1000, 6, 16)):
+        ids = torch.randint(0, e, (m, k), generator=g, dtype=torch.int32)
+        want = orc.moe_align_block_size(ids, block, e)
+        got = moe_align_block_size(ids.cuda(), block, e)
+        torch.cuda.synchronize()
+        for a, b, name in zip(got, want, ("sorted_token_ids", "expert_ids", "num_tokens_post_padded")):
+            assert torch.equal(a.cpu(), b), f"{name} M={m} E={e}"
+
+
 def test_moe_align_duplicates_skew_and_out_of_range_ids():
     from alpha_moe_b200.prologue import moe_align_block_size
     g = torch.Generator().manual_seed(0)

@@ -62,3 +62,62 @@ def test_tp2_nccl_allreduce_equals_single_gpu(tmp_path):
     mp.spawn(_worker, args=(2, _free_port(), result), nprocs=2, join=True)
     r = torch.load(result)
     assert r["rel"] <= 1e-2 and r["rel_oracle"] <= 2e-2
+
+
+def _worker_fused(rank, world, port, result_path):
+    """Fused exchange: every rank's kernel adds into all ranks' peer-mapped outputs, then this library's barrier."""
+    sys.path.insert(0, ROOT)
+    os.environ["MASTER_ADDR"] = "127.0.0.1"
+    os.environ["MASTER_PORT"] = str(port)
+    os.environ["NCCL_NVLS_ENABLE"] = "0"
+    import torch.distributed as dist
+    torch.cuda.set_device(rank)
+    dev = torch.device("cuda", rank)
+    dist.init_process_group("nccl", rank=rank, world_size=world, device_id=dev)
+    import alpha_moe  # noqa: F401
+    from alpha_moe_b200 import capi
+    from alpha_moe_b200.tp import PeerReducedLayer, shard_weights
+    from oracle import moe_oracle as orc
+    layer = PeerReducedLayer(64, 1024)
+    g = torch.Generator().manual_seed(77)
+    weights = orc.make_weights(16, 1024, 512, g)
+    full = [t.to(dev) for t in weights]
+    shard = shard_weights(*full, rank, world)
+    results = {}
+    # consecutive steps of different sizes: the two buffers alternate, stale rows of a larger earlier batch must be gone
+    for step, (m, bm, bn, wn, st) in enumerate(((40, 16, 64, 4, 3), (1, 16, 32, 8, 5), (64, 64, 64, 4, 2), (7, 8, 32, 8, 2))):
+        case = orc.make_case(16, 1024, 512, m, 5, seed=100 + m, shared=True, scaling=2.5, weights=weights)
+        sid, eid, npp = [t.to(dev) for t in case.schedule(bm)]
+        x, xs, wts = case.x.to(dev), case.x_scale.to(dev), case.topk_weights.to(dev)
+        out = layer.run(x, xs, *shard, sid, eid, npp, wts, case.top_k, bm, bn, wn, st, 2.5)
+        torch.cuda.synchronize()
+        assert capi.read_status(reset=True)[0] == 0
+        got = out.cpu().clone()
+        if rank == 0:
+            ref = torch.zeros(m, 1024, dtype=torch.bfloat16, device=dev)
+            torch.ops.alpha_moe.fused_moe_w8a8_up_down(x, xs, *full, sid, eid, npp, wts, ref, case.top_k, bm, bn, wn, st, 2.5)
+            torch.cuda.synchronize()
+            results[step] = {"rel": orc.rel_l2(got, ref.cpu()), "rel_oracle": orc.rel_l2(got, orc.run_oracle(case, bm))}
+        # every rank must hold the same sums (up to the order of the bf16 additions)
+        gathered = [torch.empty_like(out) for _ in range(world)]
+        dist.all_gather(gathered, out.contiguous())
+        for other in gathered:
+            assert orc.rel_l2(other.cpu(), got) <= 1e-2
+    if rank == 0:
+        torch.save(results, result_path)
+    dist.barrier()
+    dist.destroy_process_group()
+
+
+@pytest.mark.skipif(torch.cuda.device_count() < 2, reason="needs two GPUs")
+def test_tp2_fused_peer_reduction_equals_single_gpu(tmp_path):
+    """The exchange step fused into the kernel (reductions into every rank's peer-mapped `out` + this library's
+    cross-GPU barrier, no collective call) against the unsharded single-GPU result and the oracle, over four
+    consecutive steps of different batch sizes."""
+    import torch.multiprocessing as mp
+    result = str(tmp_path / "rf.pt")
+    mp.spawn(_worker_fused, args=(2, _free_port(), result), nprocs=2, join=True)
+    r = torch.load(result)
+    assert len(r) == 4
+    for step, v in r.items():
+        assert v["rel"] <= 1e-2 and v["rel_oracle"] <= 2e-2, (step, v)

@@ -199,3 +199,18 @@ def test_layer_entry_checks_shapes_strides_and_dtypes_before_taking_pointers():
     with pytest.raises(RuntimeError, match="CUDA"):
         fused_experts_impl(good["hidden_states"], good["w1"], good["w1_scale"], good["w2"], good["w2_scale"],
                            good["topk_weights"], good["topk_ids"], config=dict(block_m=16, block_n=32, warp_n=8, stages=3))
+
+
+def test_tensor_parallel_entry_points_reject_bad_arguments_before_any_launch():
+    from alpha_moe_b200 import capi
+    p = 0x10000
+    base = dict(x=p, x_scale=p, w=p, w_scale=p, w2=p, w2_scale=p, outs=[p, p], tp_rank=0, sid=p, eid=p, npp=p, tw=p,
+                top_k=2, M=4, K=512, N=256, E=8, sorted_num=128, block_m=16, block_n=32, warp_n=8, stages=3, scaling=1.0)
+    for bad, msg in ((dict(block_m=128, block_n=64, warp_n=4), "block_m <= 64"), (dict(tp_rank=2), "tp_rank"),
+                     (dict(outs=[p] * 9), "tp_world"), (dict(outs=[p, 0]), "null"), (dict(outs=[p, p + 2]), "aligned")):
+        with pytest.raises(capi.AlphaMoeError, match=msg):
+            capi.fused_moe_w8a8_up_down_tp(*dict(base, **bad).values())
+    for flags, rank, tmo, msg in (([p] * 9, 0, 100, "tp_world"), ([p, p], 3, 100, "tp_rank"), ([p, 0], 0, 100, "null"),
+                                  ([p, p], 0, 0, "timeout_ms"), ([p, p], 0, 5000, "timeout_ms")):
+        with pytest.raises(capi.AlphaMoeError, match=msg):
+            capi.tp_barrier(flags, rank, tmo)
