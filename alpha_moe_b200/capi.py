@@ -25,6 +25,9 @@ lib.alpha_moe_b200_fused_moe_w8a8_up_down.restype = _i
 lib.alpha_moe_b200_fused_moe_w8a8_up_down.argtypes = [_vp] * 11 + [_i] * 10 + [_f, _vp]
 lib.alpha_moe_b200_fused_moe_w8a8_up_down_tp.restype = _i
 lib.alpha_moe_b200_fused_moe_w8a8_up_down_tp.argtypes = [_vp] * 6 + [ctypes.POINTER(_vp), _i, _i] + [_vp] * 4 + [_i] * 10 + [_f, _vp]
+lib.alpha_moe_b200_tp_exchange_sum.restype = _i
+lib.alpha_moe_b200_tp_exchange_sum.argtypes = [ctypes.POINTER(_vp), _vp, _vp, ctypes.c_longlong, ctypes.c_longlong,
+                                               ctypes.POINTER(_vp), _i, _i, _i, _vp]
 lib.alpha_moe_b200_tp_barrier.restype = _i
 lib.alpha_moe_b200_tp_barrier.argtypes = [ctypes.POINTER(_vp), _i, _i, _i, _vp]
 lib.alpha_moe_b200_read_status.restype = _i
@@ -88,6 +91,14 @@ def tp_barrier(flags, tp_rank, timeout_ms=1000, stream=0) -> None:
     """Enqueues the cross-GPU barrier; `flags` = device addresses of every rank's flag array (9 uint32 each)."""
     arr = (_vp * len(flags))(*flags)
     _check(lib.alpha_moe_b200_tp_barrier(arr, len(flags), tp_rank, timeout_ms, stream))
+
+
+def tp_exchange_sum(partials, result, clear_next, count, clear_count, flags, tp_rank, timeout_ms=1000, stream=0) -> None:
+    """Enqueues barrier + sum of all ranks' partial outputs + clearing of the next partial buffer (device addresses)."""
+    pa = (_vp * len(partials))(*partials)
+    fa = (_vp * len(flags))(*flags)
+    _check(lib.alpha_moe_b200_tp_exchange_sum(pa, result, clear_next or None, count, clear_count, fa, len(partials), tp_rank,
+                                              timeout_ms, stream))
 
 
 def moe_align_block_size(topk_ids, numel, num_experts, block_m, sorted_token_ids, expert_ids,

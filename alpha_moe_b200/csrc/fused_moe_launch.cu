@@ -8,6 +8,7 @@
 #include <cuda.h>
 #include <cuda_runtime.h>
 
+#include <algorithm>
 #include <atomic>
 #include <cstdarg>
 #include <cstdio>
@@ -288,6 +289,84 @@ __global__ void tp_barrier_kernel(TpFlags flags, int world, int rank, amoe::Kern
     }
 }
 
+// Exchange step of the tensor-parallel small-batch path as one kernel: barrier over the ranks, then every rank sums
+// all ranks' partial outputs (plain 16-byte loads from the peers' buffers over NVLink, fp32 sums in rank order, so
+// that every rank gets the same bits), writes its own copy of the result and clears its partial buffer of the NEXT
+// step.  flags as in tp_barrier_kernel, plus word kMaxTpWorld + 1 = a ticket counter: the last CTA to finish advances
+// the epoch, so the epoch a launch reads at its start is stable while it runs (and the kernel replays from a graph).
+struct TpExchange {
+    const uint4* part[amoe::kMaxTpWorld];
+    uint32_t* flags[amoe::kMaxTpWorld];
+};
+__global__ void __launch_bounds__(256)
+tp_exchange_sum_kernel(TpExchange b, uint4* result, uint4* clear_next, int nvec, int nclear, int world, int rank,
+                       amoe::KernelStatus* status, long long limit_cycles) {
+    __shared__ int arrived;
+    uint32_t* mine = b.flags[rank];
+    const int t = threadIdx.x;
+    const uint32_t e = *reinterpret_cast<volatile uint32_t*>(mine + amoe::kMaxTpWorld) + 1;
+    if (t == 0) arrived = 1;
+    __syncthreads();
+    if (t < world) {
+        if (blockIdx.x == 0) {
+            __threadfence_system();
+            asm volatile("st.release.sys.global.u32 [%0], %1;" ::"l"(b.flags[t] + rank), "r"(e) : "memory");
+        }
+        const long long t0 = clock64();
+        for (;;) {
+            uint32_t seen;
+            asm volatile("ld.acquire.sys.global.u32 %0, [%1];" : "=r"(seen) : "l"(mine + t) : "memory");
+            if (static_cast<int32_t>(seen - e) >= 0) break;
+            if (clock64() - t0 > limit_cycles) {
+                arrived = 0;
+                if (atomicCAS(&status->code, amoe::ST_OK, amoe::ST_WAIT_TIMEOUT) == amoe::ST_OK) {
+                    status->block = rank;
+                    status->where = 90 + t;
+                    status->iter = static_cast<int>(e);
+                }
+                break;
+            }
+        }
+    }
+    __syncthreads();
+    const int stride = gridDim.x * blockDim.x;
+    if (arrived) {
+        for (int v = blockIdx.x * blockDim.x + t; v < nvec; v += stride) {
+            float acc[8] = {0.f, 0.f, 0.f, 0.f, 0.f, 0.f, 0.f, 0.f};
+            for (int r = 0; r < world; ++r) {
+                uint4 q;
+                asm volatile("ld.global.cg.v4.u32 {%0, %1, %2, %3}, [%4];"
+                             : "=r"(q.x), "=r"(q.y), "=r"(q.z), "=r"(q.w) : "l"(b.part[r] + v) : "memory");
+                const uint32_t w4[4] = {q.x, q.y, q.z, q.w};
+#pragma unroll
+                for (int i = 0; i < 4; ++i) {
+                    const float2 f = __bfloat1622float2(*reinterpret_cast<const __nv_bfloat162*>(&w4[i]));
+                    acc[2 * i] += f.x;
+                    acc[2 * i + 1] += f.y;
+                }
+            }
+            uint32_t o[4];
+#pragma unroll
+            for (int i = 0; i < 4; ++i) {
+                __nv_bfloat162 h = __floats2bfloat162_rn(acc[2 * i], acc[2 * i + 1]);
+                o[i] = *reinterpret_cast<uint32_t*>(&h);
+            }
+            result[v] = make_uint4(o[0], o[1], o[2], o[3]);
+        }
+    }
+    for (int v = blockIdx.x * blockDim.x + t; v < nclear; v += stride) clear_next[v] = make_uint4(0u, 0u, 0u, 0u);
+    __syncthreads();
+    if (t == 0) {
+        __threadfence();
+        const uint32_t ticket = atomicAdd(mine + amoe::kMaxTpWorld + 1, 1u);
+        if (ticket == gridDim.x - 1) {
+            mine[amoe::kMaxTpWorld + 1] = 0;
+            mine[amoe::kMaxTpWorld] = e;
+            __threadfence();
+        }
+    }
+}
+
 int launch_fused(const void* x, const float* x_scale, const void* w, const float* w_scale, const void* w2,
                  const float* w2_scale, void* const* outs, int tp_world, int tp_rank, const int32_t* sorted_token_ids,
                  const int32_t* expert_ids, const int32_t* num_tokens_post_padded, const float* topk_weights, int top_k,
@@ -442,6 +521,42 @@ int alpha_moe_b200_tp_barrier(void* const* flags, int tp_world, int tp_rank, int
     if (int rc = device_facts(dev, &facts)) return rc;
     const long long limit = static_cast<long long>(timeout_ms) * 2000000LL;      // about 2 GHz
     tp_barrier_kernel<<<1, 32, 0, static_cast<cudaStream_t>(stream)>>>(f, tp_world, tp_rank, facts.status, limit);
+    CUDA_TRY(cudaGetLastError());
+    return ALPHA_MOE_OK;
+}
+
+int alpha_moe_b200_tp_exchange_sum(void* const* partials, void* result, void* clear_next, long long count, long long clear_count,
+                                   void* const* flags, int tp_world, int tp_rank, int timeout_ms, void* stream) {
+    if (!partials || !result || !flags) return fail(ALPHA_MOE_E_ARG, "null pointer argument");
+    if (tp_world < 1 || tp_world > amoe::kMaxTpWorld || tp_rank < 0 || tp_rank >= tp_world)
+        return fail(ALPHA_MOE_E_ARG, "tp_world must be in 1..%d and 0 <= tp_rank < tp_world (got %d, %d)",
+                    amoe::kMaxTpWorld, tp_world, tp_rank);
+    if (timeout_ms < 1 || timeout_ms > 2000) return fail(ALPHA_MOE_E_ARG, "timeout_ms must be in 1..2000, got %d", timeout_ms);
+    if (count <= 0 || count % 8 != 0 || clear_count < 0 || clear_count % 8 != 0 || count > 0x3FFFFFFFLL * 8 ||
+        clear_count > 0x3FFFFFFFLL * 8)
+        return fail(ALPHA_MOE_E_ARG, "count and clear_count are bf16 element counts, multiples of 8 (got %lld, %lld)", count,
+                    clear_count);
+    if (clear_count > 0 && !clear_next) return fail(ALPHA_MOE_E_ARG, "clear_next is null");
+    TpExchange b;
+    for (int r = 0; r < amoe::kMaxTpWorld; ++r) {
+        b.part[r] = r < tp_world ? static_cast<const uint4*>(partials[r]) : nullptr;
+        b.flags[r] = r < tp_world ? static_cast<uint32_t*>(flags[r]) : nullptr;
+        if (r < tp_world && (!partials[r] || !flags[r] || (reinterpret_cast<uintptr_t>(partials[r]) & 15) ||
+                             (reinterpret_cast<uintptr_t>(flags[r]) & 3)))
+            return fail(ALPHA_MOE_E_ARG, "partial buffer or flag array of rank %d is null or misaligned", r);
+    }
+    if ((reinterpret_cast<uintptr_t>(result) & 15) || (reinterpret_cast<uintptr_t>(clear_next) & 15))
+        return fail(ALPHA_MOE_E_ARG, "result and clear_next must be 16-byte aligned");
+    int dev = 0;
+    CUDA_TRY(cudaGetDevice(&dev));
+    DeviceFacts facts;
+    if (int rc = device_facts(dev, &facts)) return rc;
+    const int nvec = static_cast<int>(count / 8), nclear = static_cast<int>(clear_count / 8);
+    int blocks = (std::max(nvec, nclear) + 255) / 256;
+    blocks = std::max(1, std::min(blocks, facts.sms));
+    const long long limit = static_cast<long long>(timeout_ms) * 2000000LL;
+    tp_exchange_sum_kernel<<<blocks, 256, 0, static_cast<cudaStream_t>(stream)>>>(
+        b, static_cast<uint4*>(result), static_cast<uint4*>(clear_next), nvec, nclear, tp_world, tp_rank, facts.status, limit);
     CUDA_TRY(cudaGetLastError());
     return ALPHA_MOE_OK;
 }

@@ -46,29 +46,41 @@ def tp_layer(compute, out: torch.Tensor, group=None) -> torch.Tensor:
 
 
 class PeerReducedLayer:
-    """Small-batch tensor parallelism without a collective call: every rank's fused kernel adds its partial result
-    straight into the `out` buffers of all ranks (peer-mapped symmetric memory, plain reductions over NVLink), and a
-    cross-GPU barrier kernel of this library closes the step.  Two output buffers are used alternately, so that a
-    step needs one barrier only: the buffer of step i+1 is cleared locally before the barrier of step i.
+    """Small-batch tensor parallelism without a collective call.  Two forms of the exchange step, both over
+    peer-mapped symmetric memory and both closed by a bounded cross-GPU barrier of this library:
 
-    Buffers come from torch.distributed._symmetric_memory (one process per GPU, NCCL process group up);
-    `max_tokens` x `hidden` bf16 per buffer.  Use for blocks of at most 64 assignments (decode-size batches); larger
-    batches run the plain operator followed by an all-reduce (`tp_layer`), whose payload the kernel would otherwise
-    send top_k times over."""
+      mode="exchange" (default)  every rank's fused kernel accumulates into its own partial buffer; ONE further kernel
+                                 then waits for all ranks, sums all ranks' partials with 16-byte loads over NVLink
+                                 (fp32, in rank order: every rank gets the same bits) and clears this rank's partial
+                                 buffer of the next step (alpha_moe_b200_tp_exchange_sum);
+      mode="epilogue"            the fused kernel's epilogue adds every partial result straight into the output buffers
+                                 of all ranks (alpha_moe_b200_fused_moe_w8a8_up_down_tp), then a barrier kernel.  This
+                                 sends every (token, expert) row to every peer as 4-byte reductions and measured
+                                 slower than an all-reduce at every batch size; it is kept as the reference point.
 
-    def __init__(self, max_tokens: int, hidden: int, group=None, timeout_ms: int = 1000):
+    Two buffers are used alternately, so that a step needs one barrier only.  Buffers come from
+    torch.distributed._symmetric_memory (one process per GPU, NCCL process group up); `max_tokens` x `hidden` bf16 each.
+    Meant for blocks of at most 64 assignments (decode-size batches); larger batches run the plain operator followed
+    by an all-reduce (`tp_layer`)."""
+
+    def __init__(self, max_tokens: int, hidden: int, group=None, timeout_ms: int = 1000, mode: str = "exchange"):
         import torch.distributed as dist
         import torch.distributed._symmetric_memory as symm_mem
+        if mode not in ("exchange", "epilogue"):
+            raise ValueError("mode must be 'exchange' or 'epilogue'")
+        if hidden % 8 != 0:
+            raise ValueError("hidden must be a multiple of 8")
         group = group or dist.group.WORLD
         self.rank, self.world = dist.get_rank(group), dist.get_world_size(group)
         if self.world > 8:
             raise ValueError("at most 8 ranks")
         dev = torch.device("cuda", torch.cuda.current_device())
-        self.max_tokens, self.hidden, self.timeout_ms = max_tokens, hidden, timeout_ms
+        self.max_tokens, self.hidden, self.timeout_ms, self.mode = max_tokens, hidden, timeout_ms, mode
         self.out = symm_mem.empty(2, max_tokens, hidden, dtype=torch.bfloat16, device=dev)
         self.flags = symm_mem.empty(16, dtype=torch.int32, device=dev)
         self.out.zero_()
         self.flags.zero_()
+        self.result = torch.zeros(2, max_tokens, hidden, dtype=torch.bfloat16, device=dev)
         torch.cuda.synchronize()
         h_out = symm_mem.rendezvous(self.out, group.group_name)
         h_flags = symm_mem.rendezvous(self.flags, group.group_name)
@@ -76,27 +88,34 @@ class PeerReducedLayer:
         self._flag_ptrs = [int(p) for p in h_flags.buffer_ptrs]
         self._handles = (h_out, h_flags)
         self._step = 0
+        nbytes = max_tokens * hidden * 2
+        self._outs = [[p + j * nbytes for p in self._out_ptrs] for j in (0, 1)]     # per buffer: every rank's address
+        self._result_ptr = [self.result[j].data_ptr() for j in (0, 1)]
         dist.barrier(group)             # every rank's buffers are zero before anyone's first step
 
     def run(self, x, x_scale, w, w_scale, w2, w2_scale, sorted_token_ids, expert_ids, num_tokens_post_padded,
             topk_weights, top_k, block_m, block_n, warp_n, stages, scaling_factor) -> torch.Tensor:
         """One layer call on this rank's weight shard; returns the full (summed over ranks) bf16 [M, K] output, a
-        view of one of the two symmetric buffers that stays valid until the call after next."""
+        view of a buffer that stays valid until the call after next."""
         from . import capi
         m, k = x.shape
         if m > self.max_tokens or k != self.hidden:
             raise ValueError(f"x is [{m}, {k}], the buffers hold [{self.max_tokens}, {self.hidden}]")
         j = self._step & 1
         self._step += 1
-        nbytes = self.max_tokens * self.hidden * 2
-        outs = [p + j * nbytes for p in self._out_ptrs]
+        outs = self._outs[j]
         stream = torch.cuda.current_stream().cuda_stream
         e, n, _ = w.shape
-        capi.fused_moe_w8a8_up_down_tp(
-            x.data_ptr(), x_scale.data_ptr(), w.data_ptr(), w_scale.data_ptr(), w2.data_ptr(), w2_scale.data_ptr(),
-            outs, self.rank, sorted_token_ids.data_ptr(), expert_ids.data_ptr(), num_tokens_post_padded.data_ptr(),
-            topk_weights.data_ptr(), top_k, m, k, n, e, sorted_token_ids.numel(), block_m, block_n, warp_n, stages,
-            float(scaling_factor), stream)
-        self.out[j ^ 1].zero_()         # the next step's buffer (all of it), cleared before this step's barrier
-        capi.tp_barrier(self._flag_ptrs, self.rank, self.timeout_ms, stream)
-        return self.out[j, :m]
+        common = (sorted_token_ids.data_ptr(), expert_ids.data_ptr(), num_tokens_post_padded.data_ptr(),
+                  topk_weights.data_ptr(), top_k, m, k, n, e, sorted_token_ids.numel(), block_m, block_n, warp_n, stages,
+                  float(scaling_factor), stream)
+        tensors = (x.data_ptr(), x_scale.data_ptr(), w.data_ptr(), w_scale.data_ptr(), w2.data_ptr(), w2_scale.data_ptr())
+        if self.mode == "epilogue":
+            capi.fused_moe_w8a8_up_down_tp(*tensors, outs, self.rank, *common)
+            self.out[j ^ 1].zero_()         # the next step's buffer (all of it), cleared before this step's barrier
+            capi.tp_barrier(self._flag_ptrs, self.rank, self.timeout_ms, stream)
+            return self.out[j, :m]
+        capi.fused_moe_w8a8_up_down(*tensors, outs[self.rank], *common)
+        capi.tp_exchange_sum(outs, self._result_ptr[j], self._outs[j ^ 1][self.rank], m * k, self.max_tokens * self.hidden,
+                             self._flag_ptrs, self.rank, self.timeout_ms, stream)
+        return self.result[j, :m]

@@ -8,8 +8,9 @@ Headline workload at every N: the DeepSeek-V3 TP8 shard per GPU (E=257 incl. the
 K=7168, I=256 per GPU, top_k=8+1, routed_scaling_factor=2.5), M=4096, i.e. N GPUs serve a layer whose
 intermediate size is 256*N ("weak" scaling; N=8 is the real DeepSeek-V3 layer, I=2048, TP8).
 Beside the headline the JSON line carries sub-records for the rest of the metric:
-  sweep    the headline shape over M = 1 ... 8192 (at N > 1 and M <= 64 also with the exchange step fused into
-           the kernel instead of the all-reduce: us_step_fused_tp)
+  sweep    the headline shape over M = 1 ... 8192 (at N > 1 and M <= 64 also with this library's own
+           exchange kernel over peer-mapped memory instead of the all-reduce call: us_step_own_exchange; *_graph =
+           the step replayed from a CUDA graph)
   qwen3    the Qwen3-Next TP2 shard (E=512, K=2048, I=256, top_k=10) over M      (1 GPU only)
   zipf     the headline shape at M=8192 with Zipf(1.2) routing                   (1 GPU only)
   tp_fixed the unsharded layer I=2048 split I/N per GPU ("strong" scaling) at M = 1, 64, 1024, 8192
@@ -436,41 +437,62 @@ def main():
         step_ms, kern_ms = max_over_ranks(step_ms, kern_ms)
         return step_ms, kern_ms, inp, knobs
 
-    def time_graph_step(wl, m, steps):
-        """The same step (clear `out` + fused kernel) replayed from a CUDA graph, as a serving engine's decode loop
-        issues it: below a few hundred tokens the eager step is bound by the host's launch path, not by the GPU."""
-        inp, d, out, call, knobs = prepare(wl, m)
+    fused_tp = {}
+
+    def time_graph_step(wl, m, steps, own_exchange=False):
+        """Two consecutive steps replayed from a CUDA graph, as a serving engine's decode loop issues them: below a few
+        hundred tokens the eager step is bound by the host's launch path, not by the GPU.  A step is: clear `out` +
+        fused kernel (+ NCCL all-reduce at N > 1), or with own_exchange (N > 1) this library's PeerReducedLayer: fused
+        kernel + barrier / sum / clear kernel over peer-mapped memory.  Returns ms per step, max over ranks."""
+        inp, d, out, call, (bm, bn, wn, st) = prepare(wl, m)
+        sh = wl.shape
+        if own_exchange:
+            from alpha_moe_b200.tp import PeerReducedLayer
+            if "layer" not in fused_tp:
+                fused_tp["layer"] = PeerReducedLayer(64, sh.k)
+            lay = fused_tp["layer"]
+
+            def one():
+                lay.run(inp["x"], inp["x_scale"], wl.w, wl.w_scale, wl.w2, wl.w2_scale, d["sid"], d["eid"], d["npp"],
+                        d["topk_weights"], sh.top_k, bm, bn, wn, st, sh.scaling)
+        else:
+            def one():
+                out.zero_()
+                call()
+                if world > 1:
+                    dist.all_reduce(out)
         s = torch.cuda.Stream()
         s.wait_stream(torch.cuda.current_stream())
         g = torch.cuda.CUDAGraph()
         with torch.cuda.stream(s):
-            out.zero_()
-            call()                                   # first call outside the capture: attributes, tensor maps
+            one()
+            one()                                    # first calls outside the capture: attributes, tensor maps
             torch.cuda.synchronize()
             with torch.cuda.graph(g, stream=s):
-                out.zero_()
-                call()
+                one()
+                one()
         torch.cuda.current_stream().wait_stream(s)
         for _ in range(3):
             g.replay()
-        torch.cuda.synchronize()
+        barrier()
         tot = 0.0
         for i in range(steps):
             flush.fill_(i & 0xFF)
+            barrier()
             e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
             e0.record()
             g.replay()
             e1.record()
             torch.cuda.synchronize()
-            tot += e0.elapsed_time(e1)
-        launches[0] += steps
-        return tot / steps
-
-    fused_tp = {}
+            tot += e0.elapsed_time(e1) / 2
+        launches[0] += 2 * steps
+        (ms,) = max_over_ranks(tot / steps)
+        return ms
 
     def time_fused_tp(wl, m, steps, warmup):
-        """Small batches on N > 1 ranks with the exchange step fused into the kernel: reductions into every rank's
-        peer-mapped `out`, clearing of the next buffer and this library's cross-GPU barrier; no collective call."""
+        """Small batches on N > 1 ranks with this library's own exchange step instead of the all-reduce call: the
+        operator accumulates into a peer-mapped partial buffer, one kernel then waits for all ranks, sums all ranks'
+        partials over NVLink and clears the next buffer (alpha_moe_b200.tp.PeerReducedLayer)."""
         from alpha_moe_b200.tp import PeerReducedLayer
         sh = wl.shape
         if "layer" not in fused_tp:
@@ -704,10 +726,11 @@ def main():
         for ms_ in SWEEP_MS:
             s_ms, k_ms, sinp, sk = time_steps(wl, ms_, 10, 3)
             extra = {}
-            if world == 1 and ms_ <= GRAPH_MAX_M:
+            if ms_ <= GRAPH_MAX_M:
                 extra["us_step_graph"] = round(time_graph_step(wl, ms_, 10) * 1e3, 1)
             if world > 1 and ms_ <= 64 and sk[0] <= 64:
-                extra["us_step_fused_tp"] = round(time_fused_tp(wl, ms_, 10, 3) * 1e3, 1)
+                extra["us_step_own_exchange"] = round(time_fused_tp(wl, ms_, 10, 3) * 1e3, 1)
+                extra["us_step_own_exchange_graph"] = round(time_graph_step(wl, ms_, 10, own_exchange=True) * 1e3, 1)
             sweep.append(sweep_record(sh, ms_, s_ms, k_ms, sinp, sk, extra))
         for ms_ in LAYER_MS:
             if world == 1:

@@ -62,13 +62,27 @@ int alpha_moe_b200_fused_moe_w8a8_up_down_tp(
     float scaling_factor, void* stream);
 
 /* Barrier over the tp_world GPUs of the fused tensor-parallel path, enqueued on `stream` (no counterpart in the
- * reference).  flags: HOST array of tp_world device pointers, flags[r] = rank r's flag array of 9 uint32 in memory
+ * reference).  flags: HOST array of tp_world device pointers, flags[r] = rank r's flag array of 10 uint32 in memory
  * that every rank can write (symmetric memory), all zero before the first barrier.  Work enqueued on this stream
  * before the barrier on every rank (the reductions of alpha_moe_b200_fused_moe_w8a8_up_down_tp, the clearing of the
  * next buffer) is complete and visible on every rank once the barrier has passed there.  The wait is bounded: after
  * timeout_ms (1..2000) the kernel records {code 1, this rank, 90 + the rank that did not arrive, epoch} in the status
  * word and returns; read it with alpha_moe_b200_read_status.  Nothing traps. */
 int alpha_moe_b200_tp_barrier(void* const* flags, int tp_world, int tp_rank, int timeout_ms, void* stream);
+
+/* Exchange step of tensor parallelism for small batches as ONE kernel of this library instead of a collective call
+ * (no counterpart in the reference; its caller all-reduces, extra/sglang.patch:38-41): barrier over the ranks, then
+ * this rank sums the partial outputs of all ranks - partials[r] = rank r's bf16 buffer of `count` elements, mapped
+ * into this GPU's address space, read with plain 16-byte loads over NVLink, summed in fp32 in rank order (every rank
+ * obtains the same bits) - into `result` (this GPU's memory, bf16, `count` elements), and clears `clear_count` bf16
+ * elements at `clear_next` (this rank's partial buffer of the NEXT step; may be NULL with clear_count 0).
+ * Use two partial buffers alternately: a rank may overwrite a partial buffer only after the exchange of the following
+ * step has passed its barrier, which the fused clear guarantees.  flags as for alpha_moe_b200_tp_barrier, 10 words per
+ * rank.  count, clear_count: multiples of 8; all buffers 16-byte aligned.  Bounded wait as in alpha_moe_b200_tp_barrier;
+ * after a run-out wait `result` is not written. */
+int alpha_moe_b200_tp_exchange_sum(void* const* partials, void* result, void* clear_next, long long count,
+                                   long long clear_count, void* const* flags, int tp_world, int tp_rank, int timeout_ms,
+                                   void* stream);
 
 /* Replaces the external moe_align_block_size the reference calls before the operator
  * (jit_moe.py:158, extra/sglang.patch:33-35).  topk_ids [numel] i32 (the flattened [M,top_k] expert

@@ -64,7 +64,7 @@ def test_tp2_nccl_allreduce_equals_single_gpu(tmp_path):
     assert r["rel"] <= 1e-2 and r["rel_oracle"] <= 2e-2
 
 
-def _worker_fused(rank, world, port, result_path):
+def _worker_fused(rank, world, port, result_path, mode):
     """Fused exchange: every rank's kernel adds into all ranks' peer-mapped outputs, then this library's barrier."""
     sys.path.insert(0, ROOT)
     os.environ["MASTER_ADDR"] = "127.0.0.1"
@@ -78,7 +78,7 @@ def _worker_fused(rank, world, port, result_path):
     from alpha_moe_b200 import capi
     from alpha_moe_b200.tp import PeerReducedLayer, shard_weights
     from oracle import moe_oracle as orc
-    layer = PeerReducedLayer(64, 1024)
+    layer = PeerReducedLayer(64, 1024, mode=mode)
     g = torch.Generator().manual_seed(77)
     weights = orc.make_weights(16, 1024, 512, g)
     full = [t.to(dev) for t in weights]
@@ -110,13 +110,15 @@ def _worker_fused(rank, world, port, result_path):
 
 
 @pytest.mark.skipif(torch.cuda.device_count() < 2, reason="needs two GPUs")
-def test_tp2_fused_peer_reduction_equals_single_gpu(tmp_path):
-    """The exchange step fused into the kernel (reductions into every rank's peer-mapped `out` + this library's
-    cross-GPU barrier, no collective call) against the unsharded single-GPU result and the oracle, over four
-    consecutive steps of different batch sizes."""
+@pytest.mark.parametrize("mode", ["exchange", "epilogue"])
+def test_tp2_exchange_without_a_collective_equals_single_gpu(tmp_path, mode):
+    """The exchange step done by this library's own kernels over peer-mapped memory, no collective call: either one
+    barrier + sum + clear kernel after the operator ("exchange"), or reductions into every rank's `out` from the
+    operator's epilogue plus a barrier kernel ("epilogue").  Against the unsharded single-GPU result and the oracle,
+    over four consecutive steps of different batch sizes (the two buffers alternate)."""
     import torch.multiprocessing as mp
     result = str(tmp_path / "rf.pt")
-    mp.spawn(_worker_fused, args=(2, _free_port(), result), nprocs=2, join=True)
+    mp.spawn(_worker_fused, args=(2, _free_port(), result, mode), nprocs=2, join=True)
     r = torch.load(result)
     assert len(r) == 4
     for step, v in r.items():

@@ -214,3 +214,9 @@ def test_tensor_parallel_entry_points_reject_bad_arguments_before_any_launch():
                                   ([p, p], 0, 0, "timeout_ms"), ([p, p], 0, 5000, "timeout_ms")):
         with pytest.raises(capi.AlphaMoeError, match=msg):
             capi.tp_barrier(flags, rank, tmo)
+    for kw, msg in ((dict(count=12), "multiples of 8"), (dict(partials=[p, p + 4]), "misaligned"), (dict(result=0), "null"),
+                    (dict(clear_next=0, clear_count=64), "clear_next")):
+        a = dict(partials=[p, p], result=p, clear_next=p, count=64, clear_count=64, flags=[p, p], tp_rank=0)
+        a.update(kw)
+        with pytest.raises(capi.AlphaMoeError, match=msg):
+            capi.tp_exchange_sum(*a.values())
