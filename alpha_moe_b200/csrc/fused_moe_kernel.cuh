@@ -55,21 +55,8 @@ struct MoeParams {
     int ksplit;                 // CTAs of a cluster that share one (block, slice): 1 (no cluster), 2, 4 or 8
     float scaling;
     KernelStatus* status;
-#ifdef AMOE_TRACE
-    long long* trace;           // [12][iterations] clock64 stamps of one CTA (debug builds only)
-    int trace_block;
-#endif
 };
 
-#ifdef AMOE_TRACE
-#define AMOE_STAMP(ev, it)                                                                   \
-    do {                                                                                     \
-        if (p.trace && static_cast<int>(blockIdx.x) == p.trace_block)                        \
-            p.trace[(ev) * NIT + (it)] = clock64();                                          \
-    } while (0)
-#else
-#define AMOE_STAMP(ev, it) do { } while (0)
-#endif
 
 constexpr int kTileBytes = 128 * 128;  // one 128-row x 128-byte operand tile
 
@@ -167,17 +154,6 @@ fused_moe_w8a8_up_down_sm100_kernel(const __grid_constant__ CUtensorMap tm_w,
     const int ND = (crank + 1) * nd_all / ks - jt_begin;                        // down-projection iterations
     const int NIT = UPI + ND;
     const int S = p.stages;
-    if (threadIdx.x == 0) AMOE_STAMP(6, 0);
-#ifdef AMOE_TRACE
-    if (p.trace && threadIdx.x == 0) {
-        unsigned long long gt;
-        asm volatile("mov.u64 %0, %%globaltimer;" : "=l"(gt));
-        unsigned smid;
-        asm volatile("mov.u32 %0, %%smid;" : "=r"(smid));
-        p.trace[4000 + blockIdx.x * 3] = static_cast<long long>(gt);
-        p.trace[4000 + blockIdx.x * 3 + 2] = smid;
-    }
-#endif
 
     // The operand tiles need 1024-byte alignment (128-byte swizzle atoms).  The dynamic shared memory
     // window is declared with that alignment; should a toolchain ever place it differently, the CTA
@@ -237,9 +213,7 @@ fused_moe_w8a8_up_down_sm100_kernel(const __grid_constant__ CUtensorMap tm_w,
     __syncthreads();
     tc_fence_after();
     const uint32_t tmem_base = *tmem_slot;
-    if (threadIdx.x == 0) AMOE_STAMP(6, 1);
     if (ks > 1) cluster_sync_all();      // no CTA may signal a peer's barriers before that peer has initialised them
-    if (threadIdx.x == 0) AMOE_STAMP(6, 2);
 
     if (warp >= W_G0) {
     // ====================================================================== control warpgroup
@@ -273,17 +247,14 @@ fused_moe_w8a8_up_down_sm100_kernel(const __grid_constant__ CUtensorMap tm_w,
                 const uint32_t aph = (it >> 1) & 1;
                 const uint32_t d0 = tmem_base + b * 2 * BMP;
                 const bool up = it < UPI;
-                AMOE_STAMP(8, it);
                 if (!up && !h_waited) {
                     if (!mbar_wait(h_ready, 0, abort_flag, p.status, 20, it)) break;
                     h_waited = true;
                 }
                 if (!mbar_wait(&acc_empty[b], aph ^ 1, abort_flag, p.status, 21, it)) break;
-                AMOE_STAMP(9, it);
                 if (!mbar_wait(&full[s], ph, abort_flag, p.status, 22, it)) break;
                 fence_proxy_async_smem();      // token rows were written by cp.async, the UMMA reads them through the async proxy
                 tc_fence_after();
-                AMOE_STAMP(1, it);
                 const uint64_t off = static_cast<uint64_t>(s * dstep);
                 if (up) {
                     umma_f8_chunk2(d0, d0 + BMP, a0_up0 + off, a1_up0 + off, x_up0 + off, x_up0 + off, idesc);
@@ -294,11 +265,9 @@ fused_moe_w8a8_up_down_sm100_kernel(const __grid_constant__ CUtensorMap tm_w,
                 } else {
                     umma_f8_chunk1(d0, a0_dn0 + off, h0, idesc);
                 }
-                AMOE_STAMP(11, it);
                 // One commit per chunk: the epilogue, once it sees the accumulators complete, also hands
                 // the ring slot back to the producers (the MMAs have finished reading it by then).
                 umma_commit(&acc_full[b]);
-                AMOE_STAMP(2, it);
                 s += step;
                 while (s >= S) { s -= S; ph ^= 1; }
             }
@@ -328,11 +297,9 @@ fused_moe_w8a8_up_down_sm100_kernel(const __grid_constant__ CUtensorMap tm_w,
         uint32_t ph = 0;
         int kc = kc_begin, sl = 0;
         for (int it = 0; it < UPI; ++it) {
-            if (tma_thread) AMOE_STAMP(7, it);
             if (!mbar_wait(&empty[s], ph ^ 1, abort_flag, p.status, 30, it)) { ok = false; break; }
             uint8_t* st = smem + s * L.stage_bytes;
             if (tma_thread) {
-                AMOE_STAMP(0, it);
                 mbar_arrive_expect_tx(&full[s], 2 * kTileBytes);
                 // 256 interleaved rows (128 gate + 128 up) of slice (slice0 + sl) x 128 bytes of K chunk kc
                 tma_load_3d(st, &tm_w, &full[s], kc * 128, (slice0 + sl) * 256, expert);
@@ -356,10 +323,8 @@ fused_moe_w8a8_up_down_sm100_kernel(const __grid_constant__ CUtensorMap tm_w,
             for (int jl = 0; jl < ND; ++jl) {
                 const int it = UPI + jl;
                 const int jt = jt_begin + jl;
-                AMOE_STAMP(7, it);
                 if (!mbar_wait(&empty[s], ph ^ 1, abort_flag, p.status, 10, it)) break;
                 uint8_t* st = smem + s * L.stage_bytes;
-                AMOE_STAMP(0, it);
                 mbar_arrive_expect_tx(&full[s], 2 * kTileBytes);
                 if (SPC == 1) {   // hidden rows [2jt*128, +256) of the slice's 128 columns; rows past K arrive as zeros
                     tma_load_3d(st, &tm_w2, &full[s], slice0 * 128, (2 * jt) * 128, expert);
@@ -413,7 +378,6 @@ fused_moe_w8a8_up_down_sm100_kernel(const __grid_constant__ CUtensorMap tm_w,
             if (tokrow[j] < p.M) nhi = j + 1;
         const int my_ncols = min(max(nhi - hh * NC, 0), NC);
         const bool few = nhi <= 2 && NEPI_WG == 1;   // at most two live columns in the whole block (CTA-uniform)
-        if (etid == 0) AMOE_STAMP(6, 3);
 
         float accg[NC], accu[NC];
 #pragma unroll
@@ -439,7 +403,6 @@ fused_moe_w8a8_up_down_sm100_kernel(const __grid_constant__ CUtensorMap tm_w,
             if (etid == 0) mbar_arrive(&empty[es]);      // the MMAs of this chunk have consumed the slot
             if (++es == S) es = 0;
             tc_fence_after();
-            if (etid == 0) AMOE_STAMP(3, it);
             const float sg = swg[sl * KC + kc], su = swu[sl * KC + kc];
             const uint32_t tb = tlane + b * 2 * BMP;
 #pragma unroll
@@ -466,10 +429,8 @@ fused_moe_w8a8_up_down_sm100_kernel(const __grid_constant__ CUtensorMap tm_w,
             tc_fence_before();
             __syncwarp();
             if (lane == 0) mbar_arrive(&acc_empty[b]);
-            if (etid == 0) AMOE_STAMP(4, it);
 
             if (++kc == kc_end) {
-                if (etid == 0) AMOE_STAMP(10, 0);
                 if (ks > 1) {
                     // ---- K-split: every CTA of the cluster holds partial sums over its own K chunks.  Publish
                     // ours in shared memory, tell every peer, wait (bounded) until all peers have published,
@@ -523,7 +484,6 @@ fused_moe_w8a8_up_down_sm100_kernel(const __grid_constant__ CUtensorMap tm_w,
                     if (!mbar_wait(xsync, 1, abort_flag, p.status, 46, it)) ok = false;
                     if (etid < ks && ok) mbar_arrive_cluster(mapa_shared(smem_u32(peer_done), etid));
                 }
-                if (etid == 0) AMOE_STAMP(10, 1);
                 // ---- end of a slice: SwiGLU, per-token amax over the slice's 128 columns, fp8 re-quantisation
                 //      (reference :936-1005; h stays in registers, only the fp8 tile goes to shared memory)
                 // Blocks of one or two tokens are the rule at small batch: then only the first two columns are
@@ -588,7 +548,6 @@ fused_moe_w8a8_up_down_sm100_kernel(const __grid_constant__ CUtensorMap tm_w,
         }
         named_bar_sync(1, EPI_THREADS);
         if (etid == 0) mbar_arrive(h_ready);
-        if (etid == 0) AMOE_STAMP(10, 2);
 
         // ---- down-projection epilogue: scale, pair adjacent hidden columns, bf16x2 reduce into out
         //      (reference :1052-1094 goes through stmatrix + per-row bulk reduce).
@@ -605,7 +564,6 @@ fused_moe_w8a8_up_down_sm100_kernel(const __grid_constant__ CUtensorMap tm_w,
             if (etid == 0) mbar_arrive_relaxed(&empty[es]);
             if (++es == S) es = 0;
             tc_fence_after();
-            if (etid == 0) AMOE_STAMP(3, it);
             const bool two = SPC == 2 || (2 * jt + 1 < KC);
             const uint32_t tb = tlane + b * 2 * BMP;
             uint32_t v0[NC], v1[NC];
@@ -620,7 +578,6 @@ fused_moe_w8a8_up_down_sm100_kernel(const __grid_constant__ CUtensorMap tm_w,
             tc_fence_before();
             __syncwarp();
             if (lane == 0) mbar_arrive_relaxed(&acc_empty[b]);
-            if (etid == 0) AMOE_STAMP(4, it);
 
             if constexpr (SPC == 1) {
                 // v0 / v1 = hidden tiles 2jt and 2jt+1 of the same slice
@@ -686,9 +643,7 @@ fused_moe_w8a8_up_down_sm100_kernel(const __grid_constant__ CUtensorMap tm_w,
                     }
                 }
             }
-            if (etid == 0) AMOE_STAMP(5, it);
         }
-        if (etid == 0) AMOE_STAMP(10, 3);
         // our partial sums must stay readable until every peer of the cluster has read them
         if (ks > 1 && etid == 0) mbar_wait_cluster(peer_done, 0, abort_flag, p.status, 44, NIT);
     }
@@ -699,13 +654,6 @@ fused_moe_w8a8_up_down_sm100_kernel(const __grid_constant__ CUtensorMap tm_w,
         tc_fence_after();
         tmem_dealloc(tmem_base, TMEM_COLS);
     }
-#ifdef AMOE_TRACE
-    if (p.trace && threadIdx.x == 0) {
-        unsigned long long gt;
-        asm volatile("mov.u64 %0, %%globaltimer;" : "=l"(gt));
-        p.trace[4000 + blockIdx.x * 3 + 1] = static_cast<long long>(gt);
-    }
-#endif
 }
 
 }  // namespace amoe

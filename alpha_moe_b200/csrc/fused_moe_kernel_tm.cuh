@@ -169,13 +169,11 @@ fused_moe_w8a8_up_down_sm100_tokmajor_kernel(const __grid_constant__ CUtensorMap
                 const uint32_t aph = (it >> 1) & 1;
                 const uint32_t d = tmem_base + b * 256;
                 const bool up = it < UPI;
-                AMOE_STAMP(8, it);
                 if (!up && !h_waited) {
                     if (!mbar_wait(h_ready, 0, abort_flag, p.status, 20, it)) break;
                     h_waited = true;
                 }
                 if (!mbar_wait(&acc_empty[b], aph ^ 1, abort_flag, p.status, 21, it)) break;
-                AMOE_STAMP(9, it);
                 // The two issuers take their turns in iteration order.  A parity wait is only meaningful while
                 // the waiter is at most one phase ahead of the barrier: waiting for fill n of a slot presumes
                 // that fill n-1 has completed.  Fill n-1 belongs to iteration it-S, which with an odd ring depth
@@ -203,7 +201,6 @@ fused_moe_w8a8_up_down_sm100_tokmajor_kernel(const __grid_constant__ CUtensorMap
                 *issue_turn = it + 1;
                 fence_proxy_async_smem();      // token rows were written by cp.async, the UMMA reads them through the async proxy
                 tc_fence_after();
-                AMOE_STAMP(1, it);
                 const uint64_t off = static_cast<uint64_t>(s * dstep);
                 if (up) {
                     umma_f8_chunk1(d, x_0 + off, w_0 + off, idesc256);           // D[token, 256 interleaved w rows]
@@ -212,9 +209,7 @@ fused_moe_w8a8_up_down_sm100_tokmajor_kernel(const __grid_constant__ CUtensorMap
                 } else {
                     umma_f8_chunk2(d, d + 128, h0, h1, w_0 + off, w_1 + off, idesc128);   // per-slice partial sums
                 }
-                AMOE_STAMP(11, it);
                 umma_commit(&acc_full[b]);
-                AMOE_STAMP(2, it);
                 s += step;
                 while (s >= S) { s -= S; ph ^= 1; }
             }
@@ -228,10 +223,8 @@ fused_moe_w8a8_up_down_sm100_tokmajor_kernel(const __grid_constant__ CUtensorMap
             uint32_t ph = 0;
             int kc = 0, sl = 0;
             for (int it = 0; it < NIT; ++it) {
-                AMOE_STAMP(7, it);
                 if (!mbar_wait(&empty[s], ph ^ 1, abort_flag, p.status, 30, it)) break;
                 uint8_t* st = smem + s * L.stage_bytes;
-                AMOE_STAMP(0, it);
                 mbar_arrive_expect_tx(&full[s], 2 * kTileBytes);
                 if (it < UPI) {
                     tma_load_3d(st, &tm_w, &full[s], kc * 128, (slice0 + sl) * 256, expert);
@@ -362,7 +355,6 @@ fused_moe_w8a8_up_down_sm100_tokmajor_kernel(const __grid_constant__ CUtensorMap
             if (etid == 0) mbar_arrive_relaxed(&empty[es]);
             if (++es == S) es = 0;
             tc_fence_after();
-            if (etid == 0) AMOE_STAMP(3, it);
             if (warp_valid) {
                 const float fg = sx * swg[sl * KC + kc], fu = sx * swu[sl * KC + kc];
                 const uint32_t tb = tlane + b * 256 + hh * 128;
@@ -384,7 +376,6 @@ fused_moe_w8a8_up_down_sm100_tokmajor_kernel(const __grid_constant__ CUtensorMap
             tc_fence_before();
             __syncwarp();
             if (lane == 0) mbar_arrive_relaxed(&acc_empty[b]);
-            if (etid == 0) AMOE_STAMP(4, it);
         }
             if (ok) {
                 // ---- end of a slice: SwiGLU, amax over the slice's 128 columns (64 here + 64 in the partner
@@ -485,7 +476,6 @@ fused_moe_w8a8_up_down_sm100_tokmajor_kernel(const __grid_constant__ CUtensorMap
             if (!mbar_wait(&acc_full[b], aph, abort_flag, p.status, 41, it)) { ok = false; break; }
             if (wg_lead) mbar_arrive_relaxed(&empty[slot]);
             tc_fence_after();
-            if (wg_lead) AMOE_STAMP(3, it);
 #pragma unroll
             for (int part = 0; part < PARTS; ++part) {
                 const int tile = SPC == 1 ? 2 * jt + (part >> 1) : jt;
@@ -521,11 +511,9 @@ fused_moe_w8a8_up_down_sm100_tokmajor_kernel(const __grid_constant__ CUtensorMap
                     tc_fence_before();
                     __syncwarp();
                     if (lane == 0) mbar_arrive_relaxed_n(&acc_empty[b], 2);   // 4 warps stand in for the barrier's 8
-                    if (wg_lead) AMOE_STAMP(4, it);
                 }
                 if (live) reduce_64(y, (SPC == 1 ? tile * 128 + (part & 1) * 64 : jt * 128 + part * 64));
             }
-            if (wg_lead) AMOE_STAMP(5, it);
         }
     }
 

@@ -53,10 +53,6 @@ using amoe_capi::fail;
     } while (0)
 
 __device__ amoe::KernelStatus g_status;
-#ifdef AMOE_TRACE
-long long* g_trace = nullptr;
-int g_trace_block = 0;
-#endif
 
 using EncodeTiledFn = CUresult (*)(CUtensorMap*, CUtensorMapDataType, cuuint32_t, void*, const cuuint64_t*,
                                    const cuuint64_t*, const cuuint32_t*, const cuuint32_t*, CUtensorMapInterleave,
@@ -444,10 +440,6 @@ int launch_fused(const void* x, const float* x_scale, const void* w, const float
     p.ksplit = ksplit;
     p.scaling = scaling_factor;
     p.status = facts.status;
-#ifdef AMOE_TRACE
-    p.trace = g_trace;
-    p.trace_block = g_trace_block;
-#endif
 
     const long long grid = nblocks * (N / 256 / spc) * ksplit;
     if (grid > 0x7FFFFFFFLL) return fail(ALPHA_MOE_E_ARG, "grid too large");
@@ -646,12 +638,6 @@ int alpha_moe_b200_fused_experts(void* hidden_states, void* x_fp8, float* x_scal
                                                  stages, scaling_factor, stream);
 }
 
-#ifdef AMOE_TRACE
-void alpha_moe_b200_debug_set_trace(long long* buf, int block) {
-    g_trace = buf;
-    g_trace_block = block;
-}
-#endif
 
 const char* alpha_moe_b200_last_error(void) { return g_last_error.c_str(); }
 const char* alpha_moe_b200_version(void) { return "alpha_moe_b200 0.1 (sm_100a)"; }

@@ -437,6 +437,31 @@ def main():
         step_ms, kern_ms = max_over_ranks(step_ms, kern_ms)
         return step_ms, kern_ms, inp, knobs
 
+    def host_us_per_call(wl, m, calls=300):
+        """CPU time of one operator call (no synchronisation inside the loop): through the torch dispatcher and
+        through the C ABI directly.  At M = 1 the kernel's HBM bound is a few microseconds, so this matters."""
+        inp, d, out, call, (bm, bn, wn, st) = prepare(wl, m)
+        sh = wl.shape
+        stream = torch.cuda.current_stream().cuda_stream
+        ptrs = (inp["x"].data_ptr(), inp["x_scale"].data_ptr(), wl.w.data_ptr(), wl.w_scale.data_ptr(), wl.w2.data_ptr(),
+                wl.w2_scale.data_ptr(), out.data_ptr(), d["sid"].data_ptr(), d["eid"].data_ptr(), d["npp"].data_ptr(),
+                d["topk_weights"].data_ptr())
+
+        def raw():
+            capi.fused_moe_w8a8_up_down(*ptrs, sh.top_k, m, sh.k, 2 * sh.inter, sh.e, inp["sid"].numel(), bm, bn, wn, st,
+                                        sh.scaling, stream)
+        res = {}
+        for name, fn in (("torch_op", call), ("c_abi", raw)):
+            fn()
+            torch.cuda.synchronize()
+            t0 = time.perf_counter()
+            for _ in range(calls):
+                fn()
+            res[name] = round((time.perf_counter() - t0) / calls * 1e6, 2)
+            torch.cuda.synchronize()
+        launches[0] += 2 * calls
+        return res
+
     fused_tp = {}
 
     def time_graph_step(wl, m, steps, own_exchange=False):
@@ -764,6 +789,8 @@ def main():
             torch.cuda.empty_cache()
             wl = Workload(sh, dev, rank)
 
+    host_us = host_us_per_call(wl, 1) if (world == 1 and not args.no_sweep) else None
+
     cpu = None
     if rank == 0 and world == 1 and not args.no_cpu:
         n_s = args.cpu_experts
@@ -797,7 +824,7 @@ def main():
             "e2e": {"value": f["flops"] * world / (e2e_ms * 1e-3) / 1e12, "unit": "TFLOP/s", "ms_per_step": e2e_ms,
                     "h2d_bytes_per_step": h2d, "d2h_bytes_per_step": d2h, "rows": e2e_how,
                     "pipeline": "copy-in / layer / copy-out of consecutive steps on three streams, two buffer sets"},
-            "gpu_launches": launches[0],
+            "gpu_launches": launches[0], "host_us_per_call_m1": host_us,
             "clocks": clocks, "kernel_status": list(status), "sweep": sweep, "layer": layer, "zipf": zipf,
             "qwen3": qwen, "tp_fixed": tp_fixed,
         }
