@@ -60,10 +60,14 @@ struct MoeParams {
 
 constexpr int kTileBytes = 128 * 128;  // one 128-row x 128-byte operand tile
 
-// bf16x2 reduction of (lo, hi) into element offset `off` of this rank's `out` and of every peer's, if row < M.
+// bf16x2 reduction of (lo, hi) into element offset `off` of this rank's `out` if row < M; with PEERS also into
+// every peer's.  (A template parameter, not a run-time test: the loop next to every 4-byte reduction cost the
+// single-GPU kernels 10-80 % when it was one.)
+template <bool PEERS>
 __device__ __forceinline__ void red_out_all_ranks(const MoeParams& p, size_t off, float lo, float hi, int row) {
     red_add_bf16x2_if(p.out + off, lo, hi, row, p.M);
-    for (int pr = 0; pr + 1 < p.tp_world; ++pr) red_add_bf16x2_if(p.out_more[pr] + off, lo, hi, row, p.M);
+    if constexpr (PEERS)
+        for (int pr = 0; pr + 1 < p.tp_world; ++pr) red_add_bf16x2_if(p.out_more[pr] + off, lo, hi, row, p.M);
 }
 
 struct SmemPlan {
@@ -93,10 +97,11 @@ __host__ __device__ inline SmemPlan smem_plan(int bmp, int s, int kc, int spc, i
     return p;
 }
 
+// PEERS: the tensor-parallel form whose epilogue adds into every rank's `out` (MoeParams::out_more).
 // EW = epilogue warpgroups.  BMP = 64 exists in two shapes: EW = 2 (one CTA per SM, deep ring) and EW = 1, whose
 // 256 threads and two-slot ring let two CTAs share an SM, so that one CTA's waits (accumulator hand-offs, the
 // switch between the two phases) are filled by the other CTA's work.
-template <int BMP, int SPC, int EW = (BMP >= 64 ? 2 : 1)>
+template <int BMP, int SPC, int EW = (BMP >= 64 ? 2 : 1), bool PEERS = false>
 __global__ void __launch_bounds__(128 * EW + 128, (BMP <= 32 || (BMP == 64 && EW == 1)) ? 2 : 1)
 fused_moe_w8a8_up_down_sm100_kernel(const __grid_constant__ CUtensorMap tm_w,
                                     const __grid_constant__ CUtensorMap tm_w2, const MoeParams p) {
@@ -610,7 +615,7 @@ fused_moe_w8a8_up_down_sm100_kernel(const __grid_constant__ CUtensorMap tm_w,
                                     const float lo = odd ? recv : a;
                                     const float hi = odd ? bb : recv;
                                     const int row = odd ? r1 : r0;
-                                    red_out_all_ranks(p, obase + static_cast<size_t>(row) * p.K, lo, hi, row);
+                                    red_out_all_ranks<PEERS>(p, obase + static_cast<size_t>(row) * p.K, lo, hi, row);
                                 }
                             }
                         }
@@ -638,7 +643,7 @@ fused_moe_w8a8_up_down_sm100_kernel(const __grid_constant__ CUtensorMap tm_w,
                             const float lo = odd ? recv : a;
                             const float hi = odd ? bb : recv;
                             const int row = odd ? rr.y : rr.x;
-                            red_out_all_ranks(p, obase + static_cast<size_t>(row) * p.K, lo, hi, row);
+                            red_out_all_ranks<PEERS>(p, obase + static_cast<size_t>(row) * p.K, lo, hi, row);
                         }
                     }
                 }

@@ -162,9 +162,9 @@ int ensure_smem_attr(Kern kern, std::atomic<int>* configured, int dev) {
     return ALPHA_MOE_OK;
 }
 
-template <int BMP, int SPC, int EW = (BMP >= 64 ? 2 : 1)>
+template <int BMP, int SPC, int EW = (BMP >= 64 ? 2 : 1), bool PEERS = false>
 int launch_variant(const MapSet& maps, const amoe::MoeParams& p, int grid, int smem_bytes, int dev, cudaStream_t stream) {
-    auto kern = amoe::fused_moe_w8a8_up_down_sm100_kernel<BMP, SPC, EW>;
+    auto kern = amoe::fused_moe_w8a8_up_down_sm100_kernel<BMP, SPC, EW, PEERS>;
     static std::atomic<int> configured[kMaxDevices];
     if (int rc = ensure_smem_attr(kern, configured, dev)) return rc;
     constexpr int threads = 128 * EW + 128;
@@ -451,6 +451,20 @@ int launch_fused(const void* x, const float* x_scale, const void* w, const float
     if (token_major(block_m))
         return spc == 1 ? launch_tokmajor<1>(maps, p, g, smem_bytes, dev, st)
                         : launch_tokmajor<2>(maps, p, g, smem_bytes, dev, st);
+    if (tp_world > 1) {       // the form that adds into the peers' buffers: one shape per tile width
+        if (spc == 1) {
+            switch (bmp) {
+                case 16: return launch_variant<16, 1, 1, true>(maps, p, g, smem_bytes, dev, st);
+                case 32: return launch_variant<32, 1, 1, true>(maps, p, g, smem_bytes, dev, st);
+                default: return launch_variant<64, 1, 2, true>(maps, p, g, smem_bytes, dev, st);
+            }
+        }
+        switch (bmp) {
+            case 16: return launch_variant<16, 2, 1, true>(maps, p, g, smem_bytes, dev, st);
+            case 32: return launch_variant<32, 2, 1, true>(maps, p, g, smem_bytes, dev, st);
+            default: return launch_variant<64, 2, 2, true>(maps, p, g, smem_bytes, dev, st);
+        }
+    }
     if (spc == 1) {
         switch (bmp) {
             case 16: return launch_variant<16, 1>(maps, p, g, smem_bytes, dev, st);
