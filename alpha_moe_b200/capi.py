@@ -28,6 +28,8 @@ lib.alpha_moe_b200_fused_moe_w8a8_up_down_tp.argtypes = [_vp] * 6 + [ctypes.POIN
 lib.alpha_moe_b200_tp_exchange_sum.restype = _i
 lib.alpha_moe_b200_tp_exchange_sum.argtypes = [ctypes.POINTER(_vp), _vp, _vp, ctypes.c_longlong, ctypes.c_longlong,
                                                ctypes.POINTER(_vp), _i, _i, _i, _vp]
+lib.alpha_moe_b200_tp_allreduce.restype = _i
+lib.alpha_moe_b200_tp_allreduce.argtypes = [ctypes.POINTER(_vp), ctypes.c_longlong, ctypes.POINTER(_vp), _i, _i, _i, _vp]
 lib.alpha_moe_b200_tp_barrier.restype = _i
 lib.alpha_moe_b200_tp_barrier.argtypes = [ctypes.POINTER(_vp), _i, _i, _i, _vp]
 lib.alpha_moe_b200_read_status.restype = _i
@@ -99,6 +101,13 @@ def tp_exchange_sum(partials, result, clear_next, count, clear_count, flags, tp_
     fa = (_vp * len(flags))(*flags)
     _check(lib.alpha_moe_b200_tp_exchange_sum(pa, result, clear_next or None, count, clear_count, fa, len(partials), tp_rank,
                                               timeout_ms, stream))
+
+
+def tp_allreduce(bufs, count, flags, tp_rank, timeout_ms=1000, stream=0) -> None:
+    """Enqueues the in-place all-reduce over the ranks' peer-mapped buffers (device addresses; count in bf16 elements)."""
+    ba = (_vp * len(bufs))(*bufs)
+    fa = (_vp * len(flags))(*flags)
+    _check(lib.alpha_moe_b200_tp_allreduce(ba, count, fa, len(bufs), tp_rank, timeout_ms, stream))
 
 
 def moe_align_block_size(topk_ids, numel, num_experts, block_m, sorted_token_ids, expert_ids,

@@ -363,6 +363,140 @@ tp_exchange_sum_kernel(TpExchange b, uint4* result, uint4* clear_next, int nvec,
     }
 }
 
+// All-reduce (sum, bf16, in place) of the ranks' partial outputs for large batches, as one kernel over peer-mapped
+// buffers: barrier; every rank sums ITS 1/world slice over all ranks (16-byte loads over NVLink, fp32, rank order) and
+// writes it back into its own buffer; second barrier; every rank copies the other slices from their owners.  Each
+// rank reads 2 (world-1)/world of the payload over NVLink, like a ring or two-shot collective, but with plain loads
+// and two flag barriers instead of a protocol.  Flags and epochs as in tp_exchange_sum_kernel (two epochs per call);
+// the "this rank has finished its slice" signal is sent by the last CTA to finish phase 1 (ticket counter).
+template <int UNROLL>
+__device__ __forceinline__ bool tp_wait_all(uint32_t* mine, int world, uint32_t e, int rank, amoe::KernelStatus* status,
+                                            long long limit_cycles, int where_base) {
+    __shared__ int arrived_s;
+    const int t = threadIdx.x;
+    if (t == 0) arrived_s = 1;
+    __syncthreads();
+    if (t < world) {
+        const long long t0 = clock64();
+        for (;;) {
+            uint32_t seen;
+            asm volatile("ld.acquire.sys.global.u32 %0, [%1];" : "=r"(seen) : "l"(mine + t) : "memory");
+            if (static_cast<int32_t>(seen - e) >= 0) break;
+            if (clock64() - t0 > limit_cycles) {
+                arrived_s = 0;
+                if (atomicCAS(&status->code, amoe::ST_OK, amoe::ST_WAIT_TIMEOUT) == amoe::ST_OK) {
+                    status->block = rank;
+                    status->where = where_base + t;
+                    status->iter = static_cast<int>(e);
+                }
+                break;
+            }
+        }
+    }
+    __syncthreads();
+    return arrived_s != 0;
+}
+__device__ __forceinline__ void tp_signal_all(const TpExchange& b, int world, int rank, uint32_t e) {
+    if (threadIdx.x < world) {
+        __threadfence_system();
+        asm volatile("st.release.sys.global.u32 [%0], %1;" ::"l"(b.flags[threadIdx.x] + rank), "r"(e) : "memory");
+    }
+}
+__device__ __forceinline__ uint4 ld_cg_v4(const uint4* p) {
+    uint4 q;
+    asm volatile("ld.global.cg.v4.u32 {%0, %1, %2, %3}, [%4];" : "=r"(q.x), "=r"(q.y), "=r"(q.z), "=r"(q.w) : "l"(p) : "memory");
+    return q;
+}
+__global__ void __launch_bounds__(256)
+tp_allreduce_kernel(TpExchange b, int nvec, int world, int rank, amoe::KernelStatus* status, long long limit_cycles) {
+    uint32_t* mine = b.flags[rank];
+    uint32_t* ticket = mine + amoe::kMaxTpWorld + 1;
+    const int t = threadIdx.x;
+    const uint32_t e0 = *reinterpret_cast<volatile uint32_t*>(mine + amoe::kMaxTpWorld);
+    uint4* own = const_cast<uint4*>(b.part[rank]);
+    if (blockIdx.x == 0) tp_signal_all(b, world, rank, e0 + 1);              // my fused kernel has finished (stream order)
+    bool ok = tp_wait_all<0>(mine, world, e0 + 1, rank, status, limit_cycles, 90);
+    const int per = (nvec + world - 1) / world;
+    const int stride = gridDim.x * blockDim.x;
+    if (ok) {
+        // phase 1: my slice, summed over all ranks, two vectors per thread and step
+        const int lo = rank * per, hi = min(nvec, lo + per);
+        for (int v = lo + blockIdx.x * blockDim.x + t; v < hi; v += 2 * stride) {
+            const int v2 = v + stride;
+            uint4 a[amoe::kMaxTpWorld], c[amoe::kMaxTpWorld];
+#pragma unroll
+            for (int r = 0; r < amoe::kMaxTpWorld; ++r) {
+                if (r < world) {
+                    a[r] = ld_cg_v4(b.part[r] + v);
+                    if (v2 < hi) c[r] = ld_cg_v4(b.part[r] + v2);
+                }
+            }
+#pragma unroll
+            for (int half = 0; half < 2; ++half) {
+                if (half == 1 && v2 >= hi) break;
+                float acc[8] = {0.f, 0.f, 0.f, 0.f, 0.f, 0.f, 0.f, 0.f};
+#pragma unroll
+                for (int r = 0; r < amoe::kMaxTpWorld; ++r) {
+                    if (r < world) {
+                        const uint4 q = half ? c[r] : a[r];
+                        const uint32_t w4[4] = {q.x, q.y, q.z, q.w};
+#pragma unroll
+                        for (int i = 0; i < 4; ++i) {
+                            const float2 f = __bfloat1622float2(*reinterpret_cast<const __nv_bfloat162*>(&w4[i]));
+                            acc[2 * i] += f.x;
+                            acc[2 * i + 1] += f.y;
+                        }
+                    }
+                }
+                uint32_t o[4];
+#pragma unroll
+                for (int i = 0; i < 4; ++i) {
+                    __nv_bfloat162 h = __floats2bfloat162_rn(acc[2 * i], acc[2 * i + 1]);
+                    o[i] = *reinterpret_cast<uint32_t*>(&h);
+                }
+                own[half ? v2 : v] = make_uint4(o[0], o[1], o[2], o[3]);
+            }
+        }
+    }
+    // the last CTA of this rank to get here tells the peers that the slice is complete
+    __shared__ int last_s;
+    __syncthreads();
+    if (t == 0) {
+        __threadfence();
+        last_s = atomicAdd(ticket, 1u) == gridDim.x - 1;
+    }
+    __syncthreads();
+    if (last_s) tp_signal_all(b, world, rank, e0 + 2);
+    ok = tp_wait_all<1>(mine, world, e0 + 2, rank, status, limit_cycles, 100) && ok;
+    if (ok) {
+        // phase 2: the other ranks' finished slices, four vectors per thread and step
+        for (int q = 1; q < world; ++q) {
+            const int r = (rank + q) % world;
+            const int lo = r * per, hi = min(nvec, lo + per);
+            const uint4* src = b.part[r];
+            for (int v = lo + blockIdx.x * blockDim.x + t; v < hi; v += 4 * stride) {
+                uint4 x0 = ld_cg_v4(src + v), x1, x2, x3;
+                if (v + stride < hi) x1 = ld_cg_v4(src + v + stride);
+                if (v + 2 * stride < hi) x2 = ld_cg_v4(src + v + 2 * stride);
+                if (v + 3 * stride < hi) x3 = ld_cg_v4(src + v + 3 * stride);
+                own[v] = x0;
+                if (v + stride < hi) own[v + stride] = x1;
+                if (v + 2 * stride < hi) own[v + 2 * stride] = x2;
+                if (v + 3 * stride < hi) own[v + 3 * stride] = x3;
+            }
+        }
+    }
+    __syncthreads();
+    if (t == 0) {
+        __threadfence();
+        if (atomicAdd(ticket, 1u) == 2 * gridDim.x - 1) {      // every CTA has passed both phases
+            *ticket = 0;
+            mine[amoe::kMaxTpWorld] = e0 + 2;
+            __threadfence();
+        }
+    }
+}
+
 int launch_fused(const void* x, const float* x_scale, const void* w, const float* w_scale, const void* w2,
                  const float* w2_scale, void* const* outs, int tp_world, int tp_rank, const int32_t* sorted_token_ids,
                  const int32_t* expert_ids, const int32_t* num_tokens_post_padded, const float* topk_weights, int top_k,
@@ -563,6 +697,37 @@ int alpha_moe_b200_tp_exchange_sum(void* const* partials, void* result, void* cl
     const long long limit = static_cast<long long>(timeout_ms) * 2000000LL;
     tp_exchange_sum_kernel<<<blocks, 256, 0, static_cast<cudaStream_t>(stream)>>>(
         b, static_cast<uint4*>(result), static_cast<uint4*>(clear_next), nvec, nclear, tp_world, tp_rank, facts.status, limit);
+    CUDA_TRY(cudaGetLastError());
+    return ALPHA_MOE_OK;
+}
+
+int alpha_moe_b200_tp_allreduce(void* const* bufs, long long count, void* const* flags, int tp_world, int tp_rank,
+                                int timeout_ms, void* stream) {
+    if (!bufs || !flags) return fail(ALPHA_MOE_E_ARG, "null pointer argument");
+    if (tp_world < 1 || tp_world > amoe::kMaxTpWorld || tp_rank < 0 || tp_rank >= tp_world)
+        return fail(ALPHA_MOE_E_ARG, "tp_world must be in 1..%d and 0 <= tp_rank < tp_world (got %d, %d)",
+                    amoe::kMaxTpWorld, tp_world, tp_rank);
+    if (timeout_ms < 1 || timeout_ms > 2000) return fail(ALPHA_MOE_E_ARG, "timeout_ms must be in 1..2000, got %d", timeout_ms);
+    if (count <= 0 || count % 8 != 0 || count > 0x3FFFFFFFLL * 8)
+        return fail(ALPHA_MOE_E_ARG, "count is a bf16 element count, a multiple of 8 (got %lld)", count);
+    TpExchange b;
+    for (int r = 0; r < amoe::kMaxTpWorld; ++r) {
+        b.part[r] = r < tp_world ? static_cast<const uint4*>(bufs[r]) : nullptr;
+        b.flags[r] = r < tp_world ? static_cast<uint32_t*>(flags[r]) : nullptr;
+        if (r < tp_world && (!bufs[r] || !flags[r] || (reinterpret_cast<uintptr_t>(bufs[r]) & 15) ||
+                             (reinterpret_cast<uintptr_t>(flags[r]) & 3)))
+            return fail(ALPHA_MOE_E_ARG, "buffer or flag array of rank %d is null or misaligned", r);
+    }
+    int dev = 0;
+    CUDA_TRY(cudaGetDevice(&dev));
+    DeviceFacts facts;
+    if (int rc = device_facts(dev, &facts)) return rc;
+    const int nvec = static_cast<int>(count / 8);
+    const int per = (nvec + tp_world - 1) / tp_world;
+    // every CTA must be resident at once (all of them wait for the peers): at most one per SM
+    const int blocks = std::max(1, std::min((per + 511) / 512, facts.sms));
+    const long long limit = static_cast<long long>(timeout_ms) * 2000000LL;
+    tp_allreduce_kernel<<<blocks, 256, 0, static_cast<cudaStream_t>(stream)>>>(b, nvec, tp_world, tp_rank, facts.status, limit);
     CUDA_TRY(cudaGetLastError());
     return ALPHA_MOE_OK;
 }

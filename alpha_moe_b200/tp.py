@@ -119,3 +119,53 @@ class PeerReducedLayer:
         capi.tp_exchange_sum(outs, self._result_ptr[j], self._outs[j ^ 1][self.rank], m * k, self.max_tokens * self.hidden,
                              self._flag_ptrs, self.rank, self.timeout_ms, stream)
         return self.result[j, :m]
+
+
+class PeerAllReduce:
+    """Two peer-mapped bf16 `out` buffers of [max_tokens, hidden] per rank and this library's own in-place all-reduce
+    over them (alpha_moe_b200_tp_allreduce: two flag barriers, every rank sums its slice of the rows and fetches the
+    others'), for batches too large for PeerReducedLayer.  A step is: `buf = ar.next_buffer(m)` (a zeroed [m, hidden]
+    view), run the operator into it, `ar.all_reduce()`; `buf` then holds the layer output on every rank and stays
+    valid until the call after next."""
+
+    def __init__(self, max_tokens: int, hidden: int, group=None, timeout_ms: int = 1000):
+        import torch.distributed as dist
+        import torch.distributed._symmetric_memory as symm_mem
+        if hidden % 8 != 0:
+            raise ValueError("hidden must be a multiple of 8")
+        group = group or dist.group.WORLD
+        self.rank, self.world = dist.get_rank(group), dist.get_world_size(group)
+        if self.world > 8:
+            raise ValueError("at most 8 ranks")
+        dev = torch.device("cuda", torch.cuda.current_device())
+        self.max_tokens, self.hidden, self.timeout_ms = max_tokens, hidden, timeout_ms
+        self.out = symm_mem.empty(2, max_tokens, hidden, dtype=torch.bfloat16, device=dev)
+        self.flags = symm_mem.empty(16, dtype=torch.int32, device=dev)
+        self.out.zero_()
+        self.flags.zero_()
+        torch.cuda.synchronize()
+        h_out = symm_mem.rendezvous(self.out, group.group_name)
+        h_flags = symm_mem.rendezvous(self.flags, group.group_name)
+        nbytes = max_tokens * hidden * 2
+        self._bufs = [[int(p) + j * nbytes for p in h_out.buffer_ptrs] for j in (0, 1)]
+        self._flag_ptrs = [int(p) for p in h_flags.buffer_ptrs]
+        self._handles = (h_out, h_flags)
+        self._step = 0
+        self._cur = None
+        dist.barrier(group)
+
+    def next_buffer(self, m: int) -> torch.Tensor:
+        if m > self.max_tokens:
+            raise ValueError(f"{m} tokens, the buffers hold {self.max_tokens}")
+        j = self._step & 1
+        self._step += 1
+        buf = self.out[j, :m]
+        buf.zero_()
+        self._cur = (j, m)
+        return buf
+
+    def all_reduce(self) -> None:
+        from . import capi
+        j, m = self._cur
+        capi.tp_allreduce(self._bufs[j], m * self.hidden, self._flag_ptrs, self.rank, self.timeout_ms,
+                          torch.cuda.current_stream().cuda_stream)

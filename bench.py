@@ -2,7 +2,8 @@
 """Benchmark of the fused W8A8 MoE layer (torch.ops.alpha_moe.fused_moe_w8a8_up_down) on B200.
 
 One "step" = one MoE layer call on one batch of M tokens: zero `out`, run the fused kernel on this
-rank's shard of the intermediate dimension, and (N > 1) all-reduce the partial bf16 outputs.
+rank's shard of the intermediate dimension, and (N > 1) all-reduce the partial bf16 outputs (with NCCL or with
+this library's own all-reduce kernel over peer-mapped buffers; the headline takes the faster, `exchange` says which).
 
 Headline workload at every N: the DeepSeek-V3 TP8 shard per GPU (E=257 incl. the shared expert,
 K=7168, I=256 per GPU, top_k=8+1, routed_scaling_factor=2.5), M=4096, i.e. N GPUs serve a layer whose
@@ -410,26 +411,43 @@ def main():
                d["topk_weights"], o, sh.top_k, bm, bn, wn, st, sh.scaling)
         return inp, d, out, call, (bm, bn, wn, st)
 
-    def time_steps(wl, m, steps, warmup, zipf=None):
-        """(ms per whole step, ms per fused-kernel launch) as the max over ranks, inputs, knobs."""
+    own_ar = {}
+
+    def peer_all_reduce(hidden):
+        """This library's all-reduce over peer-mapped output buffers (alpha_moe_b200.tp.PeerAllReduce), made once."""
+        if hidden not in own_ar:
+            from alpha_moe_b200.tp import PeerAllReduce
+            own_ar[hidden] = PeerAllReduce(max(SWEEP_MS), hidden, timeout_ms=2000)
+        return own_ar[hidden]
+
+    def time_steps(wl, m, steps, warmup, zipf=None, own_exchange=False):
+        """(ms per whole step, ms per fused-kernel launch) as the max over ranks, inputs, knobs.  The exchange step at
+        N > 1 is the NCCL all-reduce, or with own_exchange this library's all-reduce kernel over peer-mapped buffers."""
         inp, d, out, call, knobs = prepare(wl, m, zipf)
-        for _ in range(warmup):
-            out.zero_()
-            call()
-            if world > 1:
+        ar = peer_all_reduce(wl.shape.k) if (own_exchange and world > 1) else None
+
+        def one(ev=None):
+            if ev:
+                ev[0].record()
+            buf = ar.next_buffer(m) if ar else out.zero_()
+            if ev:
+                ev[1].record()
+            call(buf)
+            if ev:
+                ev[2].record()
+            if ar:
+                ar.all_reduce()
+            elif world > 1:
                 dist.all_reduce(out)
+            if ev:
+                ev[3].record()
+        for _ in range(warmup):
+            one()
         barrier()
         ev = [[torch.cuda.Event(enable_timing=True) for _ in range(4)] for _ in range(steps)]
         for i in range(steps):
             flush.fill_(i & 0xFF)                     # evict L2 between timed steps (not timed)
-            ev[i][0].record()
-            out.zero_()
-            ev[i][1].record()
-            call()
-            ev[i][2].record()
-            if world > 1:
-                dist.all_reduce(out)
-            ev[i][3].record()
+            one(ev[i])
         barrier()
         launches[0] += steps
         step_ms = sum(e[0].elapsed_time(e[3]) for e in ev) / steps
@@ -474,7 +492,7 @@ def main():
         if own_exchange:
             from alpha_moe_b200.tp import PeerReducedLayer
             if "layer" not in fused_tp:
-                fused_tp["layer"] = PeerReducedLayer(64, sh.k)
+                fused_tp["layer"] = PeerReducedLayer(64, sh.k, timeout_ms=2000)
             lay = fused_tp["layer"]
 
             def one():
@@ -521,7 +539,7 @@ def main():
         from alpha_moe_b200.tp import PeerReducedLayer
         sh = wl.shape
         if "layer" not in fused_tp:
-            fused_tp["layer"] = PeerReducedLayer(64, sh.k)
+            fused_tp["layer"] = PeerReducedLayer(64, sh.k, timeout_ms=2000)
         lay = fused_tp["layer"]
         inp, d, _, _, (bm, bn, wn, st) = prepare(wl, m)
         tot = 0.0
@@ -668,17 +686,23 @@ def main():
         return ms, h2d, d2h, ("each rank copies 1/N of the rows, all-gather in, reduce-scatter out" if split else
                               "whole batch per rank")
 
-    def tp_parity(wl, m):
+    def tp_parity(wl, m, own_exchange=False):
         """Correctness record of a multi-GPU run: after one step the all-reduced `out` is compared on sampled token rows
         with (a) the fp32 sum of the ranks' partial outputs and (b) the CPU restatement of the operator, which every
         rank evaluates for its own shard on those rows (summed over ranks).  Returns (rel-L2 a, rel-L2 b)."""
         from oracle import moe_oracle as orc
         sh = wl.shape
         inp, d, out, call, (bm, _, _, _) = prepare(wl, m)
-        out.zero_()
-        call()
+        ar = peer_all_reduce(sh.k) if (own_exchange and world > 1) else None
+        if ar:
+            out = ar.next_buffer(m)
+        else:
+            out.zero_()
+        call(out)
         part = out.float()
-        if world > 1:
+        if ar:
+            ar.all_reduce()
+        elif world > 1:
             dist.all_reduce(out)
         torch.cuda.synchronize()
         rows = torch.randperm(m, generator=torch.Generator().manual_seed(5))[: min(m, 2)]
@@ -734,9 +758,17 @@ def main():
     if sampler:
         sampler.start()
     step_ms, kern_ms, inp, knobs = time_steps(wl, m, args.steps, args.warmup)
+    exchange, step_ms_nccl, step_ms_own = None, None, None
+    if world > 1:
+        # the exchange step of the headline: the NCCL all-reduce or this library's own kernel, whichever is faster here
+        step_ms_nccl = step_ms
+        step_ms_own, kern_own, _, _ = time_steps(wl, m, args.steps, args.warmup, own_exchange=True)
+        exchange = "own all-reduce kernel over peer-mapped buffers" if step_ms_own < step_ms_nccl else "NCCL all-reduce"
+        if step_ms_own < step_ms_nccl:
+            step_ms, kern_ms = step_ms_own, kern_own
     clocks = sampler.stop() if sampler else None
     e2e_ms, h2d, d2h, e2e_how = time_e2e(wl, m, args.steps, args.warmup)
-    parity = tp_parity(wl, m) if world > 1 else None
+    parity = tp_parity(wl, m, own_exchange=(world > 1 and step_ms_own < step_ms_nccl)) if world > 1 else None
 
     f = fractions(sh, m, inp, kern_ms)
     bound = "hbm" if f["t_hbm"] >= f["t_fp8"] else "tensor"
@@ -753,6 +785,8 @@ def main():
             extra = {}
             if ms_ <= GRAPH_MAX_M:
                 extra["us_step_graph"] = round(time_graph_step(wl, ms_, 10) * 1e3, 1)
+            if world > 1 and ms_ >= 256:
+                extra["us_step_own_allreduce"] = round(time_steps(wl, ms_, 10, 3, own_exchange=True)[0] * 1e3, 1)
             if world > 1 and ms_ <= 64 and sk[0] <= 64:
                 extra["us_step_own_exchange"] = round(time_fused_tp(wl, ms_, 10, 3) * 1e3, 1)
                 extra["us_step_own_exchange_graph"] = round(time_graph_step(wl, ms_, 10, own_exchange=True) * 1e3, 1)
@@ -830,6 +864,7 @@ def main():
         }
         if parity is not None:
             line["tp_parity_rel_l2"], line["tp_parity_vs_oracle"] = round(parity[0], 5), round(parity[1], 5)
+            line["exchange"] = {"used": exchange, "ms_per_step_nccl": step_ms_nccl, "ms_per_step_own_allreduce": step_ms_own}
         if cpu:
             line["cpu_baseline"] = cpu
         print(json.dumps(line), flush=True)

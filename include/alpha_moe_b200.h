@@ -84,6 +84,19 @@ int alpha_moe_b200_tp_exchange_sum(void* const* partials, void* result, void* cl
                                    long long clear_count, void* const* flags, int tp_world, int tp_rank, int timeout_ms,
                                    void* stream);
 
+/* In-place all-reduce (sum, bf16) of the ranks' partial outputs as ONE kernel of this library, for batches whose
+ * payload is too large for alpha_moe_b200_tp_exchange_sum's every-rank-reads-everything (no counterpart in the
+ * reference).  bufs[r] = rank r's buffer of `count` bf16 elements, mapped into this GPU's address space; on return
+ * (stream order) bufs[tp_rank] holds the sum over all ranks, the same bits on every rank.  Two phases with a bounded
+ * flag barrier before each: every rank sums its 1/tp_world slice over all ranks and writes it back into its own
+ * buffer, then copies the other slices from their owners; each rank reads 2 (tp_world-1)/tp_world of the payload over
+ * NVLink with plain 16-byte loads.  flags as for alpha_moe_b200_tp_barrier (10 zeroed uint32 per rank, shared with
+ * the other tensor-parallel entry points).  Use two buffers alternately: a rank may clear and refill a buffer only
+ * after the all-reduce of the following step has started everywhere, which stream order gives when the next step uses
+ * the other buffer.  count: multiple of 8; buffers 16-byte aligned. */
+int alpha_moe_b200_tp_allreduce(void* const* bufs, long long count, void* const* flags, int tp_world, int tp_rank,
+                                int timeout_ms, void* stream);
+
 /* Replaces the external moe_align_block_size the reference calls before the operator
  * (jit_moe.py:158, extra/sglang.patch:33-35).  topk_ids [numel] i32 (the flattened [M,top_k] expert
  * ids; ids outside [0,num_experts) are ignored).  Outputs: sorted_token_ids

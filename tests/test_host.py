@@ -220,3 +220,6 @@ def test_tensor_parallel_entry_points_reject_bad_arguments_before_any_launch():
         a.update(kw)
         with pytest.raises(capi.AlphaMoeError, match=msg):
             capi.tp_exchange_sum(*a.values())
+    for bufs, count, msg in (([p, p], 12, "multiple of 8"), ([p, p + 8], 64, "misaligned"), ([p] * 9, 64, "tp_world")):
+        with pytest.raises(capi.AlphaMoeError, match=msg):
+            capi.tp_allreduce(bufs, count, [p] * len(bufs), 0)
