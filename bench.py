@@ -612,8 +612,30 @@ def main():
             torch.cuda.synchronize()
             if i >= warmup:
                 tot += e0.elapsed_time(e1)
-        launches[0] += steps
-        return tot / steps
+        launches[0] += 3 * steps
+        if m > GRAPH_MAX_M:
+            return tot / steps, None
+        # the same sequence replayed from a CUDA graph (the three launches of the eager call are host-bound at this size)
+        s_ = torch.cuda.Stream()
+        s_.wait_stream(torch.cuda.current_stream())
+        g = torch.cuda.CUDAGraph()
+        with torch.cuda.stream(s_):
+            stream = s_.cuda_stream
+            with torch.cuda.graph(g, stream=s_):
+                call()
+        torch.cuda.current_stream().wait_stream(s_)
+        gtot = 0.0
+        for i in range(steps):
+            hs.copy_(x0)
+            flush.fill_(i & 0xFF)
+            e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+            e0.record()
+            g.replay()
+            e1.record()
+            torch.cuda.synchronize()
+            gtot += e0.elapsed_time(e1)
+        launches[0] += 3 * steps
+        return tot / steps, gtot / steps
 
     def time_e2e(wl, m, steps, warmup):
         """Same step through the public operator with HOST inputs: every step copies its pinned x / scales / routing
@@ -814,7 +836,11 @@ def main():
             sweep.append(sweep_record(sh, ms_, s_ms, k_ms, sinp, sk, extra))
         for ms_ in LAYER_MS:
             if world == 1:
-                layer.append({"M": ms_, "us_layer": round(time_layer(wl, ms_, 6, 3) * 1e3, 1)})
+                t_eager, t_graph = time_layer(wl, ms_, 6, 3)
+                rec = {"M": ms_, "us_layer": round(t_eager * 1e3, 1)}
+                if t_graph is not None:
+                    rec["us_layer_graph"] = round(t_graph * 1e3, 1)
+                layer.append(rec)
         if world == 1:
             s_ms, k_ms, sinp, sk = time_steps(wl, 8192, 6, 3, zipf=1.2)
             counts = torch.bincount(sinp["ids"].reshape(-1).long(), minlength=sh.e)[:-1]
