@@ -497,8 +497,8 @@ def main():
     fused_tp = {}
 
     def time_graph_step(wl, m, steps, own_exchange=False):
-        """Two consecutive steps replayed from a CUDA graph, as a serving engine's decode loop issues them: below a few
-        hundred tokens the eager step is bound by the host's launch path, not by the GPU.  A step is: clear `out` +
+        """The step replayed from a CUDA graph, as a serving engine's decode loop issues it: below a few hundred
+        tokens the eager step is bound by the host's launch path, not by the GPU.  A step is: clear `out` +
         fused kernel (+ NCCL all-reduce at N > 1), or with own_exchange (N > 1) this library's PeerReducedLayer: fused
         kernel + barrier / sum / clear kernel over peer-mapped memory.  Returns ms per step, max over ranks."""
         inp, d, out, call, (bm, bn, wn, st) = prepare(wl, m)
@@ -520,32 +520,35 @@ def main():
                 call()
                 if world > 1:
                     dist.all_reduce(out)
+        # One step per graph, two graphs replayed alternately (the own exchange alternates between two buffers), the
+        # L2 flushed before every replay: a second step inside the same graph would find the first one's weights in L2.
         s = torch.cuda.Stream()
         s.wait_stream(torch.cuda.current_stream())
-        g = torch.cuda.CUDAGraph()
+        graphs = [torch.cuda.CUDAGraph(), torch.cuda.CUDAGraph()]
         with torch.cuda.stream(s):
             one()
             one()                                    # first calls outside the capture: attributes, tensor maps
             torch.cuda.synchronize()
-            with torch.cuda.graph(g, stream=s):
-                one()
-                one()
+            for g in graphs:
+                with torch.cuda.graph(g, stream=s):
+                    one()
         torch.cuda.current_stream().wait_stream(s)
-        for _ in range(3):
-            g.replay()
+        for i in range(4):
+            graphs[i & 1].replay()
         barrier()
         tot = 0.0
-        for i in range(steps):
+        for i in range(2 * steps):
             flush.fill_(i & 0xFF)
             barrier()
             e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
             e0.record()
-            g.replay()
+            graphs[i & 1].replay()
             e1.record()
             torch.cuda.synchronize()
-            tot += e0.elapsed_time(e1) / 2
+            tot += e0.elapsed_time(e1)
         launches[0] += 2 * steps
-        (ms,) = max_over_ranks(tot / steps)
+        del graphs, g                                # before any communicator is torn down
+        (ms,) = max_over_ranks(tot / (2 * steps))
         return ms
 
     def time_fused_tp(wl, m, steps, warmup):
