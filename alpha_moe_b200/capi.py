@@ -158,7 +158,8 @@ def read_status(reset: bool = False):
 def plan(K: int, block_m: int, stages: int, block_n: int = 32, N: int = 512, num_blocks: int = 1 << 20,
          num_sms: int = 148):
     """(ring_depth, padded_block_m, dynamic_smem_bytes, slices_per_cta, ksplit, kernel) the launcher uses;
-    kernel: 0 weight-major, 1 token-major."""
+    kernel: 0 weight-major, 1 token-major.  num_sms = 0 asks the current device for its cluster capacity (as a
+    launch does); a positive count models it and touches no device."""
     buf = (ctypes.c_int32 * 6)()
     _check(lib.alpha_moe_b200_plan(K, N, block_m, block_n, stages, num_blocks, num_sms, buf))
     return tuple(buf)

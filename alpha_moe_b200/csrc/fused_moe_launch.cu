@@ -119,10 +119,14 @@ int get_maps(int device, const void* w, const void* w2, int E, int N, int K, Map
     return ALPHA_MOE_OK;
 }
 
-// Facts about a device that never change, looked up once: the SM count and the address of the status word.
+constexpr int kMaxKsplit = 8;        // portable cluster size limit
+
+// Facts about a device that never change, looked up once: the SM count, the address of the status word and how many
+// clusters of 2..8 CTAs of the small-batch kernel (one CTA per SM) the device can hold at the same time.
 struct DeviceFacts {
     int sms = 0;
     amoe::KernelStatus* status = nullptr;
+    int clusters[kMaxKsplit + 1] = {};
 };
 constexpr int kMaxDevices = 64;
 
@@ -199,6 +203,15 @@ int launch_tokmajor(const MapSet& maps, const amoe::MoeParams& p, int grid, int 
     return ALPHA_MOE_OK;
 }
 
+// Without a device to ask: GPCs of about 18 SMs, a cluster inside one GPC, one CTA per SM.
+void model_cluster_capacity(int sms, int* clusters) {
+    const int gpcs = sms >= 18 ? (sms + 9) / 18 : 1;
+    const int per_gpc = sms / gpcs;
+    clusters[0] = 0;
+    clusters[1] = sms;
+    for (int ks = 2; ks <= kMaxKsplit; ++ks) clusters[ks] = gpcs * (per_gpc / ks);
+}
+
 int device_facts(int dev, DeviceFacts* out) {
     static DeviceFacts facts[kMaxDevices];
     static std::mutex mu;
@@ -207,6 +220,29 @@ int device_facts(int dev, DeviceFacts* out) {
     DeviceFacts& f = dev < kMaxDevices ? facts[dev] : local;
     if (!f.status) {
         CUDA_TRY(cudaDeviceGetAttribute(&f.sms, cudaDevAttrMultiProcessorCount, dev));
+        model_cluster_capacity(f.sms, f.clusters);
+        // The driver knows how the SMs are grouped (a cluster lives inside one GPC): ask it, keep the model's figure
+        // where it does not answer.  Asked for the narrow weight-major shape with a ring that leaves room for one
+        // CTA per SM, which is what the small-batch launches use.
+        auto kern = amoe::fused_moe_w8a8_up_down_sm100_kernel<16, 1>;
+        if (cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, kMaxDynSmem) == cudaSuccess) {
+            for (int ks = 2; ks <= kMaxKsplit; ++ks) {
+                cudaLaunchConfig_t cfg = {};
+                cfg.gridDim = dim3(static_cast<unsigned>(ks * 64));
+                cfg.blockDim = dim3(256);
+                cfg.dynamicSmemBytes = static_cast<size_t>(kPairDynSmem + 1024);
+                cudaLaunchAttribute attr;
+                attr.id = cudaLaunchAttributeClusterDimension;
+                attr.val.clusterDim.x = static_cast<unsigned>(ks);
+                attr.val.clusterDim.y = 1;
+                attr.val.clusterDim.z = 1;
+                cfg.attrs = &attr;
+                cfg.numAttrs = 1;
+                int n = 0;
+                if (cudaOccupancyMaxActiveClusters(&n, kern, &cfg) == cudaSuccess && n > 0) f.clusters[ks] = n;
+            }
+        }
+        (void)cudaGetLastError();
         CUDA_TRY(cudaGetSymbolAddress(reinterpret_cast<void**>(&f.status), g_status));
     }
     *out = f;
@@ -236,16 +272,18 @@ __global__ void wait_selftest_kernel(amoe::KernelStatus* status, int* result, lo
 
 std::atomic<int> g_ksplit_override{0};     // 0 = automatic; set through alpha_moe_b200_set_ksplit (tuners, tests)
 
-// Clusters of 2 or 4 CTAs along K for small batches: as many as still fit one CTA per SM (narrow tile, one slice
-// per CTA only; 8 is accepted as an override but measured no faster than 4).
-int choose_ksplit(int block_m, int spc, long long nblocks, int N, int K, int sms) {
+// Clusters of CTAs along K for small batches (narrow tile, one slice per CTA only): the largest cluster size for
+// which every (block, slice) unit of the launch still gets its cluster at once.  clusters[ks] = how many clusters of
+// ks CTAs the device holds at the same time; a launch with more units than that runs in two rounds and loses more
+// than the split gains (34 units at the DeepSeek shard shape: clusters of 3 34 us, of 4 49 us).
+int choose_ksplit(int block_m, int spc, long long nblocks, int N, int K, const int* clusters) {
     if (block_m > 32 || spc != 1) return 1;
-    int ksplit = 1;
-    const long long live_max = nblocks * (N / 256);
-    while (ksplit < 4 && live_max * ksplit * 2 <= sms && ksplit * 2 <= K / 128) ksplit *= 2;
+    const long long units = nblocks * (N / 256);
     const int v = g_ksplit_override.load(std::memory_order_relaxed);
-    if ((v == 1 || v == 2 || v == 4 || v == 8) && v <= K / 128) ksplit = v;
-    return ksplit;
+    if (v >= 1 && v <= kMaxKsplit && v <= K / 128) return v;
+    for (int ks = kMaxKsplit; ks >= 2; --ks)
+        if (ks <= K / 128 && units <= clusters[ks]) return ks;
+    return 1;
 }
 
 // Cross-GPU barrier of the fused tensor-parallel path.  flags[r] = rank r's flag array (kMaxTpWorld + 1 words of
@@ -543,7 +581,7 @@ int launch_fused(const void* x, const float* x_scale, const void* w, const float
     // Live blocks never exceed the number of assignments, so no more CTAs than that are launched.
     long long nblocks = (static_cast<long long>(sorted_num) + block_m - 1) / block_m;
     if (nblocks > static_cast<long long>(M) * top_k) nblocks = static_cast<long long>(M) * top_k;
-    const int ksplit = choose_ksplit(block_m, spc, nblocks, N, K, facts.sms);
+    const int ksplit = choose_ksplit(block_m, spc, nblocks, N, K, facts.clusters);
     int depth, bmp, smem_bytes;
     if (int rc = plan(K, block_m, stages, spc, ksplit, &depth, &bmp, &smem_bytes)) return rc;
 
@@ -746,8 +784,8 @@ int alpha_moe_b200_selftest_wait_timeout(int limit_cycles, int where, int iter, 
 }
 
 int alpha_moe_b200_set_ksplit(int ksplit) {
-    if (ksplit != 0 && ksplit != 1 && ksplit != 2 && ksplit != 4 && ksplit != 8)
-        return fail(ALPHA_MOE_E_ARG, "ksplit must be 0 (automatic), 1, 2, 4 or 8, got %d", ksplit);
+    if (ksplit < 0 || ksplit > kMaxKsplit)
+        return fail(ALPHA_MOE_E_ARG, "ksplit must be 0 (automatic) or 1..8 CTAs per cluster, got %d", ksplit);
     g_ksplit_override.store(ksplit, std::memory_order_relaxed);
     return ALPHA_MOE_OK;
 }
@@ -776,9 +814,19 @@ int alpha_moe_b200_plan(int K, int N, int block_m, int block_n, int stages, int 
     if (block_m < 8 || block_m > 128 || block_m % 8 != 0) return fail(ALPHA_MOE_E_ARG, "bad block_m %d", block_m);
     if (block_n != 32 && block_n != 64) return fail(ALPHA_MOE_E_ARG, "block_n must be 32 or 64, got %d", block_n);
     if (stages < 1 || stages > 5) return fail(ALPHA_MOE_E_ARG, "stages must be in 1..5, got %d", stages);
-    if (num_blocks <= 0 || num_sms <= 0) return fail(ALPHA_MOE_E_ARG, "num_blocks and num_sms must be positive");
+    if (num_blocks <= 0 || num_sms < 0) return fail(ALPHA_MOE_E_ARG, "num_blocks must be positive, num_sms >= 0");
     const int spc = (block_n == 64 && (N / 256) % 2 == 0) ? 2 : 1;
-    const int ksplit = choose_ksplit(block_m, spc, num_blocks, N, K, num_sms);
+    int clusters[kMaxKsplit + 1];
+    if (num_sms == 0) {           // the current device, as a launch would see it
+        int dev = 0;
+        CUDA_TRY(cudaGetDevice(&dev));
+        DeviceFacts facts;
+        if (int rc = device_facts(dev, &facts)) return rc;
+        for (int i = 0; i <= kMaxKsplit; ++i) clusters[i] = facts.clusters[i];
+    } else {
+        model_cluster_capacity(num_sms, clusters);
+    }
+    const int ksplit = choose_ksplit(block_m, spc, num_blocks, N, K, clusters);
     int depth, bmp, smem_bytes;
     if (int rc = plan(K, block_m, stages, spc, ksplit, &depth, &bmp, &smem_bytes)) return rc;
     out6[0] = depth;

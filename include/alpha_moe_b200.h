@@ -164,14 +164,17 @@ int alpha_moe_b200_selftest_wait_timeout(int limit_cycles, int where, int iter, 
 
 /* What the launcher uses for a problem and a knob tuple; for tuners and tests.  It runs the launcher's own
  * planning code.  num_blocks = live upper bound of schedule blocks, min(ceil(sorted_num / block_m), M * top_k);
- * num_sms = SM count of the device (148 on B200).  out6 = {ring_depth, padded_block_m, dynamic_smem_bytes,
- * slices_per_cta (2 when block_n = 64 and N/256 is even), ksplit (CTAs per cluster along K, small batches),
- * kernel (0 weight-major, 1 token-major)}.  No device work. */
+ * num_sms = SM count of a device (148 on B200): the cluster capacity that decides ksplit is then modelled (GPCs of
+ * about 18 SMs, one CTA per SM) and nothing touches a device; num_sms = 0 = the current device, whose driver is asked
+ * as a launch would (launches nothing).  out6 = {ring_depth, padded_block_m, dynamic_smem_bytes,
+ * slices_per_cta (2 when block_n = 64 and N/256 is even), ksplit (CTAs per cluster along K, small batches: the
+ * largest of 2..8 for which all (block, slice) units get their cluster at the same time, else 1),
+ * kernel (0 weight-major, 1 token-major)}. */
 int alpha_moe_b200_plan(int K, int N, int block_m, int block_n, int stages, int num_blocks, int num_sms,
                         int32_t* out6);
 
 /* Tuning hook (tuners, tests): forces the number of CTAs per cluster along K for small batches; 0 = automatic
- * choice (the default), otherwise 1, 2, 4 or 8.  Process-wide.  No counterpart in the reference. */
+ * choice (the default), otherwise 1..8.  Process-wide.  No counterpart in the reference. */
 int alpha_moe_b200_set_ksplit(int ksplit);
 
 const char* alpha_moe_b200_last_error(void);

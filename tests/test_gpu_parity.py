@@ -196,7 +196,7 @@ def ksplit_override():
     capi.set_ksplit(0)
 
 
-@pytest.mark.parametrize("ks", [1, 2, 4, 8])
+@pytest.mark.parametrize("ks", [1, 2, 3, 4, 5, 6, 7, 8])
 def test_k_split_over_a_cluster_small_batches(ks, ksplit_override):
     """Small batches: each (block, slice) is shared by a cluster of ks CTAs that split K and exchange partial
     sums through distributed shared memory.  alpha_moe_b200_set_ksplit overrides the automatic choice."""
@@ -212,6 +212,25 @@ def test_k_split_over_a_cluster_small_batches(ks, ksplit_override):
     # K with a chunk count that does not divide by ks, and an odd number of hidden tiles
     case = orc.make_case(8, 1152, 128, 2, 2, seed=9)
     check_close(run_capi(case, 16, 32, 8, 3), orc.run_oracle(case, 16), tag=f"ks={ks} K=1152")
+
+
+def test_automatic_cluster_size_follows_the_devices_cluster_capacity():
+    """The launcher asks the driver how many clusters of 2..8 CTAs the device holds at once and takes the largest
+    size at which every (block, slice) unit gets its cluster in one round; plan(num_sms=0) reports that choice.  It
+    must be monotone in the number of blocks, stay within the K chunks, and the operator must be right with it."""
+    from alpha_moe_b200 import capi
+    capi.set_ksplit(0)
+    chosen = [capi.plan(7168, 16, 5, 32, N=512, num_blocks=nb, num_sms=0)[4] for nb in range(1, 80)]
+    assert all(1 <= ks <= 8 for ks in chosen) and chosen == sorted(chosen, reverse=True)
+    assert chosen[0] >= 4 and chosen[-1] == 1
+    sms = torch.cuda.get_device_properties(0).multi_processor_count
+    for nb, ks in enumerate(chosen, start=1):
+        assert ks == 1 or 2 * nb * ks <= sms            # one CTA per SM: never more CTAs than SMs
+    assert capi.plan(256, 16, 5, 32, N=512, num_blocks=1, num_sms=0)[4] == 2
+    w = test_deepseek_shard_shape_small_expert_count.weights
+    for m, top_k in ((1, 5), (2, 5), (3, 5), (5, 4)):
+        case = orc.make_case(16, 7168, 256, m, top_k, seed=70 + m, shared=True, scaling=2.5, weights=w)
+        check_close(run_capi(case, 16, 32, 8, 5), orc.run_oracle(case, 16), tag=f"auto ks M={m}")
 
 
 def test_every_token_to_one_expert_many_blocks_of_the_same_weights():

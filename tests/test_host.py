@@ -118,13 +118,15 @@ def test_plan_fits_shared_memory_for_every_knob():
                             assert smem <= 232448
                             assert spc == (2 if bn == 64 and (n // 256) % 2 == 0 else 1)
                             assert kern == (0 if bm <= 64 else 1)
-                            assert ks in (1, 2, 4) and (ks == 1 or (bm <= 32 and spc == 1 and nblocks == 9))
+                            assert 1 <= ks <= min(8, k // 128) and (ks == 1 or (bm <= 32 and spc == 1 and nblocks == 9))
     assert capi.plan(7168, 16, 5)[0] == 5
-    # a handful of live blocks at the DeepSeek shard shape: clusters of four CTAs along K
-    assert capi.plan(7168, 16, 5, 32, N=512, num_blocks=9)[4] == 4
-    assert capi.plan(7168, 16, 5, 32, N=512, num_blocks=40)[4] == 1
+    # A handful of live blocks at the DeepSeek shard shape (two slices each): the largest cluster along K whose
+    # copies all fit the device at once, modelled here as 8 GPCs of 18 SMs (a positive num_sms touches no device).
+    for nblocks, want in ((1, 8), (8, 8), (9, 6), (12, 6), (13, 4), (16, 4), (17, 3), (24, 3), (25, 2), (36, 2), (37, 1)):
+        assert capi.plan(7168, 16, 5, 32, N=512, num_blocks=nblocks)[4] == want, nblocks
+    assert capi.plan(256, 16, 5, 32, N=512, num_blocks=1)[4] == 2       # never more CTAs than K chunks
     with pytest.raises(capi.AlphaMoeError):
-        capi.set_ksplit(3)
+        capi.set_ksplit(9)
 
 
 def test_out_alignment_is_checked_per_kernel_before_anything_is_launched():
