@@ -14,8 +14,8 @@
 //     land in the same TMEM lane and SwiGLU is thread-local;
 //   * each 128-deep K chunk is accumulated into its own TMEM buffer and promoted into fp32
 //     registers with the (128x128 weight block) x (token, 128-group) scales (reference :915-933
-//     promotes into bf16); TMEM buffers are double-buffered so chunk k+1's MMAs overlap chunk k's
-//     promotion;
+//     promotes into bf16); there are 2 to 8 such buffers (acc_buffers) so that the MMAs of the
+//     following chunks overlap chunk k's promotion;
 //   * roles: 2 gather warps (token rows by cp.async with the 128-byte swizzle applied by hand; lane 0
 //     of the first one also issues the weight TMA), 2 UMMA-issuing warps that take alternate chunks
 //     (one thread cannot issue eight UMMAs plus its barrier traffic fast enough to keep the tensor
@@ -70,6 +70,12 @@ __device__ __forceinline__ void red_out_all_ranks(const MoeParams& p, size_t off
         for (int pr = 0; pr + 1 < p.tp_world; ++pr) red_add_bf16x2_if(p.out_more[pr] + off, lo, hi, row, p.M);
 }
 
+// Accumulator buffers in tensor memory (each: two accumulators x BMP columns).  The chain of one K chunk - operands
+// landed, UMMAs issued, completion seen by the epilogue, read-back, buffer handed back - takes well over a thousand
+// cycles while its UMMAs need about a hundred at these widths, so a narrow tile keeps as many chunks in flight as
+// fit 256 columns (two CTAs of that size can share an SM's 512).
+__host__ __device__ constexpr int acc_buffers(int bmp) { return bmp <= 16 ? 8 : bmp == 32 ? 4 : 2; }
+
 struct SmemPlan {
     uint32_t stage_bytes, hq, xs, swg, swu, sw2, tokrow, topkw, tokscale, amax, part, bars, misc, total;
 };
@@ -91,7 +97,7 @@ __host__ __device__ inline SmemPlan smem_plan(int bmp, int s, int kc, int spc, i
     p.tokscale = o;  o += spc * bmp * 4;
     p.amax = o;      o += bmp * 8;
     p.part = o;      o += ksplit > 1 ? 2 * bmp * 128 * 4 : 0;
-    p.bars = o;      o += (2 * s + 10) * 8;
+    p.bars = o;      o += (2 * s + 2 * acc_buffers(bmp) + 6) * 8;
     p.misc = o;      o += 16;
     p.total = o;
     return p;
@@ -109,7 +115,8 @@ fused_moe_w8a8_up_down_sm100_kernel(const __grid_constant__ CUtensorMap tm_w,
     constexpr int NC = BMP / NEPI_WG;
     constexpr int EPI_THREADS = 128 * NEPI_WG;
     constexpr int W_G0 = 4 * NEPI_WG, W_MMA0 = W_G0 + 2;   // control warpgroup: gather, gather, UMMA, UMMA
-    constexpr uint32_t TMEM_COLS = 4 * BMP;      // two buffers x two accumulators x BMP columns
+    constexpr int NB = acc_buffers(BMP);         // accumulator buffers (chunks in flight between UMMA and epilogue)
+    constexpr uint32_t TMEM_COLS = NB * 2 * BMP; // buffers x two accumulators x BMP columns
     static_assert(BMP == 16 || BMP == 32 || BMP == 64 || BMP == 128, "padded block_m");
     static_assert(SPC == 1 || SPC == 2, "slices per CTA");
 
@@ -182,8 +189,8 @@ fused_moe_w8a8_up_down_sm100_kernel(const __grid_constant__ CUtensorMap tm_w,
     uint64_t* full = reinterpret_cast<uint64_t*>(smem + L.bars);      // slot filled: TMA bytes + 64 gather threads
     uint64_t* empty = full + S;                                       // slot free again
     uint64_t* acc_full = empty + S;
-    uint64_t* acc_empty = acc_full + 2;
-    uint64_t* h_ready = acc_empty + 2;
+    uint64_t* acc_empty = acc_full + NB;
+    uint64_t* h_ready = acc_empty + NB;
     uint64_t* xchg = h_ready + 1;                                     // [2] amax exchange inside an epilogue warpgroup
     uint64_t* peer_ready = xchg + 2;                                  // every CTA of the cluster has published its partial sums
     uint64_t* peer_done = peer_ready + 1;                             // every CTA of the cluster has finished reading ours
@@ -191,13 +198,14 @@ fused_moe_w8a8_up_down_sm100_kernel(const __grid_constant__ CUtensorMap tm_w,
     float* part = reinterpret_cast<float*>(smem + L.part);            // [2][BMP][128] this CTA's partial gate / up sums
     uint32_t* tmem_slot = reinterpret_cast<uint32_t*>(smem + L.misc);
     volatile int* abort_flag = reinterpret_cast<volatile int*>(smem + L.misc + 4);
+    volatile int* issue_turn = reinterpret_cast<volatile int*>(smem + L.misc + 8);   // chunks whose operands have been waited for
 
     if (threadIdx.x == W_G0 * 32) {
         for (int i = 0; i < S; ++i) {
             mbar_init(&full[i], 1 + 64);
             mbar_init(&empty[i], 1);
         }
-        for (int i = 0; i < 2; ++i) {
+        for (int i = 0; i < NB; ++i) {
             mbar_init(&acc_full[i], 1);
             mbar_init(&acc_empty[i], 4 * NEPI_WG);
         }
@@ -208,6 +216,7 @@ fused_moe_w8a8_up_down_sm100_kernel(const __grid_constant__ CUtensorMap tm_w,
         mbar_init(peer_done, ks);
         mbar_init(xsync, 4 * NEPI_WG);
         *abort_flag = 0;
+        *issue_turn = 0;
         fence_mbar_init();
     }
     if (warp == W_MMA0) {
@@ -248,8 +257,8 @@ fused_moe_w8a8_up_down_sm100_kernel(const __grid_constant__ CUtensorMap tm_w,
             uint32_t ph = 0;
             bool h_waited = false;
             for (int it = pw; it < NIT && pw < step; it += step) {
-                const int b = it & 1;                                       // TMEM buffer of this chunk
-                const uint32_t aph = (it >> 1) & 1;
+                const int b = it & (NB - 1);                                // TMEM buffer of this chunk
+                const uint32_t aph = (it / NB) & 1;
                 const uint32_t d0 = tmem_base + b * 2 * BMP;
                 const bool up = it < UPI;
                 if (!up && !h_waited) {
@@ -257,7 +266,31 @@ fused_moe_w8a8_up_down_sm100_kernel(const __grid_constant__ CUtensorMap tm_w,
                     h_waited = true;
                 }
                 if (!mbar_wait(&acc_empty[b], aph ^ 1, abort_flag, p.status, 21, it)) break;
+                // The two issuers wait for their operands in chunk order.  A parity wait is only meaningful while
+                // the waiter is at most one phase ahead of the barrier: waiting for fill n of a slot presumes that
+                // fill n-1 has completed.  With an odd ring depth fill n-1 belongs to the other issuer's chunk
+                // it - S, and with NB accumulator buffers this issuer may be NB chunks ahead of the epilogue, i.e.
+                // further ahead of the other issuer than the ring is deep.
+                if (step == 2) {
+                    const long long t0 = clock64();
+                    bool turn_ok = true;
+                    while (*issue_turn < it) {
+                        if (*abort_flag) { turn_ok = false; break; }
+                        if (clock64() - t0 > kWaitLimitCycles) {
+                            *abort_flag = 1;
+                            if (atomicCAS(&p.status->code, ST_OK, ST_WAIT_TIMEOUT) == ST_OK) {
+                                p.status->block = blockIdx.x;
+                                p.status->where = 23;
+                                p.status->iter = it;
+                            }
+                            turn_ok = false;
+                            break;
+                        }
+                    }
+                    if (!turn_ok) break;
+                }
                 if (!mbar_wait(&full[s], ph, abort_flag, p.status, 22, it)) break;
+                *issue_turn = it + 1;
                 fence_proxy_async_smem();      // token rows were written by cp.async, the UMMA reads them through the async proxy
                 tc_fence_after();
                 const uint64_t off = static_cast<uint64_t>(s * dstep);
@@ -270,9 +303,10 @@ fused_moe_w8a8_up_down_sm100_kernel(const __grid_constant__ CUtensorMap tm_w,
                 } else {
                     umma_f8_chunk1(d0, a0_dn0 + off, h0, idesc);
                 }
-                // One commit per chunk: the epilogue, once it sees the accumulators complete, also hands
-                // the ring slot back to the producers (the MMAs have finished reading it by then).
+                // Two commits per chunk: the accumulators are complete (for the epilogue), and the MMAs have
+                // finished reading the ring slot (for the producers, who need not wait for the epilogue).
                 umma_commit(&acc_full[b]);
+                umma_commit(&empty[s]);
                 s += step;
                 while (s >= S) { s -= S; ph ^= 1; }
             }
@@ -397,16 +431,13 @@ fused_moe_w8a8_up_down_sm100_kernel(const __grid_constant__ CUtensorMap tm_w,
 
         const uint32_t tlane = tmem_base + (static_cast<uint32_t>(q * 32) << 16) + hh * NC;
         bool ok = true;
-        int es = 0;                          // ring slot of the chunk being retired (for handing it back)
         int kc = kc_begin, sl = 0;
         uint32_t xph = 0;
         // ---- up-projection: promote each K chunk with its scales (reference :915-933)
         for (int it = 0; it < UPI && ok; ++it) {
-            const int b = it & 1;
-            const uint32_t aph = (it >> 1) & 1;
+            const int b = it & (NB - 1);
+            const uint32_t aph = (it / NB) & 1;
             if (!mbar_wait(&acc_full[b], aph, abort_flag, p.status, 40, it)) { ok = false; break; }
-            if (etid == 0) mbar_arrive(&empty[es]);      // the MMAs of this chunk have consumed the slot
-            if (++es == S) es = 0;
             tc_fence_after();
             const float sg = swg[sl * KC + kc], su = swu[sl * KC + kc];
             const uint32_t tb = tlane + b * 2 * BMP;
@@ -545,8 +576,16 @@ fused_moe_w8a8_up_down_sm100_kernel(const __grid_constant__ CUtensorMap tm_w,
                 if (few) swiglu_quant(std::integral_constant<int, (NC < 2 ? NC : 2)>{});
                 else swiglu_quant(std::integral_constant<int, NC>{});
                 fence_proxy_async_smem();
-                // (amax_part is rewritten at the end of the next slice; the acc_empty hand-shake keeps the four
-                //  warps within two chunks of each other, so every read above has long completed by then)
+                if constexpr (SPC == 2) {
+                    // amax_part is rewritten at the end of the next slice, and with several accumulator buffers a warp
+                    // may get there before another has read this slice's maxima: a second round of the same barrier
+                    if (sl == 0) {
+                        __syncwarp();
+                        if (lane == 0) mbar_arrive(&xchg[hh]);
+                        if (!mbar_wait(&xchg[hh], xph, abort_flag, p.status, 47, it)) ok = false;
+                        xph ^= 1;
+                    }
+                }
                 kc = kc_begin;
                 ++sl;
             }
@@ -563,11 +602,9 @@ fused_moe_w8a8_up_down_sm100_kernel(const __grid_constant__ CUtensorMap tm_w,
         for (int jl = 0; jl < ND && ok; ++jl) {
             const int it = UPI + jl;
             const int jt = jt_begin + jl;            // hidden-tile pair (SPC = 1) / hidden tile (SPC = 2) of the whole layer
-            const int b = it & 1;
-            const uint32_t aph = (it >> 1) & 1;
+            const int b = it & (NB - 1);
+            const uint32_t aph = (it / NB) & 1;
             if (!mbar_wait(&acc_full[b], aph, abort_flag, p.status, 41, it)) { ok = false; break; }
-            if (etid == 0) mbar_arrive_relaxed(&empty[es]);
-            if (++es == S) es = 0;
             tc_fence_after();
             const bool two = SPC == 2 || (2 * jt + 1 < KC);
             const uint32_t tb = tlane + b * 2 * BMP;
