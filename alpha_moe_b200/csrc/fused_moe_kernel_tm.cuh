@@ -210,6 +210,7 @@ fused_moe_w8a8_up_down_sm100_tokmajor_kernel(const __grid_constant__ CUtensorMap
                     umma_f8_chunk2(d, d + 128, h0, h1, w_0 + off, w_1 + off, idesc128);   // per-slice partial sums
                 }
                 umma_commit(&acc_full[b]);
+                umma_commit(&empty[s]);        // the ring slot is free once these MMAs have read it
                 s += step;
                 while (s >= S) { s -= S; ph ^= 1; }
             }
@@ -342,7 +343,6 @@ fused_moe_w8a8_up_down_sm100_tokmajor_kernel(const __grid_constant__ CUtensorMap
 
         const uint32_t tlane = tmem_base + (static_cast<uint32_t>(q * 32) << 16);
         bool ok = true;
-        int es = 0;
         uint32_t xph = 0;
         // ---- up-projection: promote each K chunk with its scales (reference :915-933).  The chunk loop is kept
         // small and contiguous (the slice-end code follows it instead of sitting inside it).
@@ -352,8 +352,6 @@ fused_moe_w8a8_up_down_sm100_tokmajor_kernel(const __grid_constant__ CUtensorMap
             const uint32_t aph = (it >> 1) & 1;
             const float sx = xs[kc * kTmRows + t];
             if (!mbar_wait(&acc_full[b], aph, abort_flag, p.status, 40, it)) { ok = false; break; }
-            if (etid == 0) mbar_arrive_relaxed(&empty[es]);
-            if (++es == S) es = 0;
             tc_fence_after();
             if (warp_valid) {
                 const float fg = sx * swg[sl * KC + kc], fu = sx * swu[sl * KC + kc];
@@ -465,16 +463,12 @@ fused_moe_w8a8_up_down_sm100_tokmajor_kernel(const __grid_constant__ CUtensorMap
         // 64 hidden columns: SPC = 2 -> 2 parts of hidden tile jt (columns [0,128) of the buffer are slice 0's
         // partial sums, [128,256) slice 1's); SPC = 1 -> 4 parts covering hidden tiles 2jt and 2jt+1.
         constexpr int PARTS = SPC == 1 ? 4 : 2;
-        const bool wg_lead = q == 0 && lane == 0;
         for (int jt = 0; jt < ND && ok; ++jt) {
             const int it = UPI + jt;
             const int b = it & 1;
             const uint32_t aph = (it >> 1) & 1;
-            const int slot = es;
-            if (++es == S) es = 0;
             if ((jt & 1) != hh) continue;
             if (!mbar_wait(&acc_full[b], aph, abort_flag, p.status, 41, it)) { ok = false; break; }
-            if (wg_lead) mbar_arrive_relaxed(&empty[slot]);
             tc_fence_after();
 #pragma unroll
             for (int part = 0; part < PARTS; ++part) {
