@@ -46,6 +46,8 @@ lib.alpha_moe_b200_align_workspace_bytes.restype = ctypes.c_int64
 lib.alpha_moe_b200_align_workspace_bytes.argtypes = [_i, _i]
 lib.alpha_moe_b200_per_token_group_quant_fp8.restype = _i
 lib.alpha_moe_b200_per_token_group_quant_fp8.argtypes = [_vp, _vp, _vp, _i, _i, _i, _vp]
+lib.alpha_moe_b200_quant_and_align.restype = _i
+lib.alpha_moe_b200_quant_and_align.argtypes = [_vp, _vp, _vp, _i, _i, _i, _vp, _i, _i, _i, _vp, _vp, _vp, _vp, _vp]
 lib.alpha_moe_b200_fused_experts.argtypes = [_vp] * 9 + [_i] * 5 + [_vp] * 4 + [_i] * 4 + [_f, _vp]
 lib.alpha_moe_b200_fused_experts.restype = _i
 lib.alpha_moe_b200_selftest_wait_timeout.restype = _i
@@ -126,6 +128,14 @@ def moe_align_block_size_noalloc(topk_ids, numel, num_experts, block_m, sorted_t
 
 def align_workspace_bytes(numel: int, num_experts: int) -> int:
     return int(lib.alpha_moe_b200_align_workspace_bytes(numel, num_experts))
+
+
+def quant_and_align(x_bf16, x_fp8, x_scale, M, K, zero_src, topk_ids, top_k, num_experts, block_m, sorted_token_ids,
+                    expert_ids, num_tokens_post_padded, workspace=None, stream=0) -> None:
+    """Quantisation of the activations and the block schedule, as one launch when M * top_k <= 1024."""
+    _check(lib.alpha_moe_b200_quant_and_align(x_bf16, x_fp8, x_scale, M, K, int(zero_src), topk_ids, top_k, num_experts,
+                                              block_m, sorted_token_ids, expert_ids, num_tokens_post_padded, workspace,
+                                              stream))
 
 
 def per_token_group_quant_fp8(x_bf16, x_fp8, x_scale, M, K, zero_src=False, stream=0) -> None:

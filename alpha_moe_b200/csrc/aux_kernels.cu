@@ -169,11 +169,10 @@ moe_align_chunks_kernel(const int32_t* ids, int numel, int E, int block, int32_t
 }
 
 // Everything in one CTA when there is a single chunk (numel <= kChunk: e.g. up to 113 tokens at top_k = 9).
-__global__ void __launch_bounds__(kAlignThreads)
-moe_align_single_kernel(const int32_t* ids, int numel, int E, int block, int32_t* sorted, int sorted_len,
-                        int32_t* expert_ids, int n_blocks_max, int32_t* num_post_pad) {
-    __shared__ int cnt[8 * kMaxExperts];
-    __shared__ int start[kMaxExperts + 1];
+// cnt: 8 * kMaxExperts ints, start: kMaxExperts + 1 ints of shared memory.
+__device__ __forceinline__ void align_single_body(const int32_t* ids, int numel, int E, int block, int32_t* sorted,
+                                                  int sorted_len, int32_t* expert_ids, int n_blocks_max,
+                                                  int32_t* num_post_pad, int* cnt, int* start) {
     for (int i = threadIdx.x; i < sorted_len; i += kAlignThreads) sorted[i] = numel;
     for (int i = threadIdx.x; i < n_blocks_max; i += kAlignThreads) expert_ids[i] = 0;
     count_chunk(ids, numel, 0, E, cnt);
@@ -209,18 +208,26 @@ moe_align_single_kernel(const int32_t* ids, int numel, int E, int block, int32_t
     scatter_chunk(ids, numel, 0, E, cnt, sorted);
 }
 
+__global__ void __launch_bounds__(kAlignThreads)
+moe_align_single_kernel(const int32_t* ids, int numel, int E, int block, int32_t* sorted, int sorted_len,
+                        int32_t* expert_ids, int n_blocks_max, int32_t* num_post_pad) {
+    __shared__ int cnt[8 * kMaxExperts];
+    __shared__ int start[kMaxExperts + 1];
+    align_single_body(ids, numel, E, block, sorted, sorted_len, expert_ids, n_blocks_max, num_post_pad, cnt, start);
+}
+
 // ------------------------------------------------------------------------------------------------
 // Per-(token, 128-group) fp8 quantisation: scale = max(amax, 1e-10) / 448, q = e4m3_rn(clamp(x / scale)).
 // Eight lanes per group, 16 elements per lane: two 16-byte loads in, one 16-byte store out (algorithmic traffic
 // 3 bytes per element, + 2 when the source is zeroed); a warp takes four consecutive groups per step and the grid
 // strides over the tensor.  The quotients are the correctly rounded IEEE ones, so the result is bit-identical to the
 // CPU restatement.
-__global__ void __launch_bounds__(256)
-group_quant_fp8_kernel(__nv_bfloat16* x, uint8_t* q, float* scale, long long n_groups, int zero_src) {
+__device__ __forceinline__ void group_quant_body(__nv_bfloat16* x, uint8_t* q, float* scale, long long n_groups,
+                                                 int zero_src, int block, int nblocks) {
     const int lane = threadIdx.x & 31;
     const int sub = lane & 7;                   // 16-element piece of the group
-    const long long warp0 = static_cast<long long>(blockIdx.x) * 8 + (threadIdx.x >> 5);
-    const long long nwarps = static_cast<long long>(gridDim.x) * 8;
+    const long long warp0 = static_cast<long long>(block) * 8 + (threadIdx.x >> 5);
+    const long long nwarps = static_cast<long long>(nblocks) * 8;
     // the loads of the next step are issued before the arithmetic of the current one (one step = 32 bytes per lane)
     uint4 n0 = make_uint4(0u, 0u, 0u, 0u), n1 = n0;
     {
@@ -292,6 +299,29 @@ group_quant_fp8_kernel(__nv_bfloat16* x, uint8_t* q, float* scale, long long n_g
             }
         }
     }
+}
+
+__global__ void __launch_bounds__(256)
+group_quant_fp8_kernel(__nv_bfloat16* x, uint8_t* q, float* scale, long long n_groups, int zero_src) {
+    group_quant_body(x, q, scale, n_groups, zero_src, blockIdx.x, gridDim.x);
+}
+
+// The two steps in front of the operator at a serving call site - quantise the activations (and clear their buffer,
+// which the layer then accumulates into) and build the block schedule - are independent of each other.  For decode-
+// size batches, whose schedule fits one CTA, they run as one launch: the last CTA builds the schedule, the others
+// quantise.  Same code, same bits as the two separate kernels.
+__global__ void __launch_bounds__(256)
+quant_and_align_small_kernel(__nv_bfloat16* x, uint8_t* q, float* scale, long long n_groups, int zero_src,
+                             const int32_t* ids, int numel, int E, int block, int32_t* sorted, int sorted_len,
+                             int32_t* expert_ids, int n_blocks_max, int32_t* num_post_pad) {
+    __shared__ int cnt[8 * kMaxExperts];
+    __shared__ int start[kMaxExperts + 1];
+    static_assert(kAlignThreads == 256, "one block shape for both halves");
+    if (blockIdx.x == gridDim.x - 1) {
+        align_single_body(ids, numel, E, block, sorted, sorted_len, expert_ids, n_blocks_max, num_post_pad, cnt, start);
+        return;
+    }
+    group_quant_body(x, q, scale, n_groups, zero_src, blockIdx.x, gridDim.x - 1);
 }
 
 // Scratch of the entry point that allocates nothing: the per-chunk histogram table lives here instead of
@@ -412,6 +442,40 @@ int alpha_moe_b200_per_token_group_quant_fp8(void* x_bf16, void* x_fp8, float* x
     if (blocks > static_cast<long long>(sms) * 8) blocks = static_cast<long long>(sms) * 8;
     group_quant_fp8_kernel<<<static_cast<unsigned>(blocks), 256, 0, static_cast<cudaStream_t>(stream)>>>(
         static_cast<__nv_bfloat16*>(x_bf16), static_cast<uint8_t*>(x_fp8), x_scale, n_groups, zero_src);
+    AUX_TRY(cudaGetLastError());
+    return ALPHA_MOE_OK;
+}
+
+int alpha_moe_b200_quant_and_align(void* x_bf16, void* x_fp8, float* x_scale, int M, int K, int zero_src,
+                                   const int32_t* topk_ids, int top_k, int num_experts, int block_m,
+                                   int32_t* sorted_token_ids, int32_t* expert_ids, int32_t* num_tokens_post_padded,
+                                   void* workspace, void* stream) {
+    using namespace amoe_aux;
+    if (M <= 0 || top_k <= 0) return fail(ALPHA_MOE_E_ARG, "M and top_k must be positive");
+    const long long numel = static_cast<long long>(M) * top_k;
+    if (numel > 0x7FFFFFFFLL) return fail(ALPHA_MOE_E_ARG, "M*top_k overflows int32");
+    if (numel > kChunk) {        // two launches: the schedule needs several CTAs and a grid-wide barrier
+        if (int rc = alpha_moe_b200_per_token_group_quant_fp8(x_bf16, x_fp8, x_scale, M, K, zero_src, stream)) return rc;
+        return alpha_moe_b200_moe_align_block_size(topk_ids, static_cast<int>(numel), num_experts, block_m,
+                                                   sorted_token_ids, expert_ids, num_tokens_post_padded, workspace, stream);
+    }
+    if (!x_bf16 || !x_fp8 || !x_scale || !topk_ids || !sorted_token_ids || !expert_ids || !num_tokens_post_padded)
+        return fail(ALPHA_MOE_E_ARG, "null pointer argument");
+    if (K <= 0 || K % 128 != 0) return fail(ALPHA_MOE_E_ARG, "need M > 0 and K a positive multiple of 128");
+    if ((reinterpret_cast<uintptr_t>(x_bf16) & 15) || (reinterpret_cast<uintptr_t>(x_fp8) & 15))
+        return fail(ALPHA_MOE_E_ARG, "x_bf16 and x_fp8 must be 16-byte aligned");
+    if (num_experts <= 0 || num_experts > kMaxExperts)
+        return fail(ALPHA_MOE_E_ARG, "num_experts must be in 1..%d (got %d)", kMaxExperts, num_experts);
+    if (block_m <= 0) return fail(ALPHA_MOE_E_ARG, "block_m must be positive (got %d)", block_m);
+    const long long sorted_len = numel + static_cast<long long>(num_experts) * (block_m - 1);
+    if (sorted_len > 0x7FFFFFFFLL) return fail(ALPHA_MOE_E_ARG, "schedule too long for int32 indices");
+    const int n_blocks_max = static_cast<int>((sorted_len + block_m - 1) / block_m);
+    const long long n_groups = static_cast<long long>(M) * (K / 128);
+    const long long qblocks = (n_groups + 31) / 32;      // at most 1024 * K / 4096 blocks: no cap needed
+    quant_and_align_small_kernel<<<static_cast<unsigned>(qblocks + 1), 256, 0, static_cast<cudaStream_t>(stream)>>>(
+        static_cast<__nv_bfloat16*>(x_bf16), static_cast<uint8_t*>(x_fp8), x_scale, n_groups, zero_src, topk_ids,
+        static_cast<int>(numel), num_experts, block_m, sorted_token_ids, static_cast<int>(sorted_len), expert_ids,
+        n_blocks_max, num_tokens_post_padded);
     AUX_TRY(cudaGetLastError());
     return ALPHA_MOE_OK;
 }

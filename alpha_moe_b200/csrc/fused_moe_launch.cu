@@ -851,12 +851,11 @@ int alpha_moe_b200_fused_experts(void* hidden_states, void* x_fp8, float* x_scal
     const long long numel = static_cast<long long>(M) * top_k;
     const long long sorted_num = numel + static_cast<long long>(num_experts) * (block_m - 1);
     if (sorted_num > 0x7FFFFFFFLL) return fail(ALPHA_MOE_E_ARG, "schedule too long for int32");
-    // extra/sglang.patch:30-31: quantise, then clear the buffer the layer accumulates into
-    if (int rc = alpha_moe_b200_per_token_group_quant_fp8(hidden_states, x_fp8, x_scale, M, K, 1, stream)) return rc;
-    // :33-35
-    if (int rc = alpha_moe_b200_moe_align_block_size(topk_ids, static_cast<int>(numel), num_experts, block_m,
-                                                      sorted_token_ids, expert_ids, num_tokens_post_padded,
-                                                      align_workspace, stream))
+    // extra/sglang.patch:30-31: quantise, then clear the buffer the layer accumulates into; :33-35: the schedule
+    // (one launch for both when the schedule fits one CTA)
+    if (int rc = alpha_moe_b200_quant_and_align(hidden_states, x_fp8, x_scale, M, K, 1, topk_ids, top_k, num_experts,
+                                                block_m, sorted_token_ids, expert_ids, num_tokens_post_padded,
+                                                align_workspace, stream))
         return rc;
     // :38-40
     return alpha_moe_b200_fused_moe_w8a8_up_down(x_fp8, x_scale, w, w_scale, w2, w2_scale, hidden_states, sorted_token_ids,

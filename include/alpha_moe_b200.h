@@ -133,6 +133,17 @@ int alpha_moe_b200_moe_align_block_size_noalloc(const int32_t* topk_ids, int num
 int alpha_moe_b200_per_token_group_quant_fp8(void* x_bf16, void* x_fp8, float* x_scale, int M, int K,
                                              int zero_src, void* stream);
 
+/* The two steps in front of the operator at the reference's call sites - the quantisation above (jit_moe.py:142,
+ * extra/sglang.patch:30-31) and the block schedule (jit_moe.py:158, extra/sglang.patch:33-35) - are independent of
+ * each other.  This entry runs both: as ONE launch when the schedule fits one CTA (M * top_k <= 1024: decode-size
+ * batches, where a launch costs about as much as either step), otherwise as the two launches above.  Outputs are
+ * bit-identical to alpha_moe_b200_per_token_group_quant_fp8 + alpha_moe_b200_moe_align_block_size with the same
+ * arguments (numel = M * top_k; workspace as for that entry, unused for M * top_k <= 1024). */
+int alpha_moe_b200_quant_and_align(void* x_bf16, void* x_fp8, float* x_scale, int M, int K, int zero_src,
+                                   const int32_t* topk_ids, int top_k, int num_experts, int block_m,
+                                   int32_t* sorted_token_ids, int32_t* expert_ids, int32_t* num_tokens_post_padded,
+                                   void* workspace, void* stream);
+
 /* The whole call-site sequence of the reference's serving patch as one call (extra/sglang.patch:25-40, the body
  * it gives fused_experts_impl): quantise the bf16 activations per token and 128-group, clear them (the layer's
  * output accumulates into the same buffer), build the block schedule for `block_m`, run the fused operator.

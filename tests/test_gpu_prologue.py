@@ -79,6 +79,28 @@ def test_group_quant_matches_oracle_bit_for_bit(m, k):
     assert (xd == 0).all()
 
 
+@pytest.mark.parametrize("m,e,k,hidden,block", [(1, 257, 9, 7168, 16), (7, 8, 2, 128, 8), (64, 512, 10, 2048, 16),
+                                                (113, 257, 9, 7168, 32), (114, 257, 9, 7168, 16), (500, 37, 9, 1024, 64)])
+def test_quant_and_align_in_one_call_matches_oracle_bit_for_bit(m, e, k, hidden, block):
+    """Quantisation and schedule as one launch (M * top_k <= 1024: the first four cases) or as the two separate
+    launches (the last two), against the CPU restatement of each; with and without clearing the source."""
+    from alpha_moe_b200.prologue import quant_and_align
+    g = torch.Generator().manual_seed(3 * m + e)
+    x = (torch.randn(m, hidden, generator=g) * torch.rand(m, 1, generator=g) * 3).to(torch.bfloat16)
+    x[0, :128] = 0
+    ids, _ = orc.route_topk(torch.randn(m, e, generator=g), k)
+    want_q, want_s = orc.quant_token_groups(x)
+    want_sched = orc.moe_align_block_size(ids, block, e)
+    for zero in (False, True):
+        xd = x.cuda()
+        q, s, sid, eid, npp = quant_and_align(xd, ids.cuda(), block, e, zero_input=zero)
+        torch.cuda.synchronize()
+        assert torch.equal(q.cpu().view(torch.uint8), want_q.view(torch.uint8)) and torch.equal(s.cpu(), want_s)
+        for a, b, name in zip((sid, eid, npp), want_sched, ("sorted_token_ids", "expert_ids", "num_tokens_post_padded")):
+            assert torch.equal(a.cpu(), b), name
+        assert (xd == 0).all() if zero else torch.equal(xd.cpu(), x)
+
+
 def test_call_site_sequence_end_to_end():
     """quantise -> zero the activations -> schedule -> fused operator accumulating into the activation
     buffer, exactly the sequence of the reference's call site (extra/sglang.patch:30-41)."""
