@@ -41,6 +41,10 @@ using amoe_capi::fail;
 // One launch runs all three phases with a grid-wide barrier after phase A (a cooperative launch, used whenever all
 // chunks fit on the GPU at once); otherwise phase A and phases B + C are two launches of the same kernel.  When
 // everything fits one chunk the phases run inside one CTA of an ordinary launch.
+// Programmatic dependent launch: the kernel behind this one in the stream (the fused operator, which is launched with
+// the matching attribute and waits for this kernel's completion before it reads anything) may be scheduled from here on.
+__device__ __forceinline__ void launch_dependents() { asm volatile("griddepcontrol.launch_dependents;" ::: "memory"); }
+
 constexpr int kChunk = 1024;          // assignments per CTA (8 warps x 4 rounds x 32 lanes)
 constexpr int kAlignThreads = 256;
 constexpr int kMaxExperts = 1024;     // per-warp counters live in shared memory: 8 x E ints
@@ -96,6 +100,7 @@ moe_align_chunks_kernel(const int32_t* ids, int numel, int E, int block, int32_t
     __shared__ int cnt[8 * kMaxExperts];
     __shared__ int warp_tot[kAlignThreads / 32];
     const int chunks = gridDim.x, chunk = blockIdx.x;
+    launch_dependents();
     if (phases & kPhaseA) {
         const int gtid = chunk * kAlignThreads + threadIdx.x, gsz = chunks * kAlignThreads;
         for (int i = gtid; i < sorted_len; i += gsz) sorted[i] = numel;
@@ -213,6 +218,7 @@ moe_align_single_kernel(const int32_t* ids, int numel, int E, int block, int32_t
                         int32_t* expert_ids, int n_blocks_max, int32_t* num_post_pad) {
     __shared__ int cnt[8 * kMaxExperts];
     __shared__ int start[kMaxExperts + 1];
+    launch_dependents();
     align_single_body(ids, numel, E, block, sorted, sorted_len, expert_ids, n_blocks_max, num_post_pad, cnt, start);
 }
 
@@ -303,6 +309,7 @@ __device__ __forceinline__ void group_quant_body(__nv_bfloat16* x, uint8_t* q, f
 
 __global__ void __launch_bounds__(256)
 group_quant_fp8_kernel(__nv_bfloat16* x, uint8_t* q, float* scale, long long n_groups, int zero_src) {
+    launch_dependents();
     group_quant_body(x, q, scale, n_groups, zero_src, blockIdx.x, gridDim.x);
 }
 
@@ -317,6 +324,7 @@ quant_and_align_small_kernel(__nv_bfloat16* x, uint8_t* q, float* scale, long lo
     __shared__ int cnt[8 * kMaxExperts];
     __shared__ int start[kMaxExperts + 1];
     static_assert(kAlignThreads == 256, "one block shape for both halves");
+    launch_dependents();      // the operator behind this launch may be scheduled; it waits for our completion
     if (blockIdx.x == gridDim.x - 1) {
         align_single_body(ids, numel, E, block, sorted, sorted_len, expert_ids, n_blocks_max, num_post_pad, cnt, start);
         return;

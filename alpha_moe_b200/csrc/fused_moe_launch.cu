@@ -166,31 +166,42 @@ int ensure_smem_attr(Kern kern, std::atomic<int>* configured, int dev) {
     return ALPHA_MOE_OK;
 }
 
+// Every fused kernel is launched with programmatic stream serialisation: its CTAs may be scheduled while the kernel
+// in front of it in the stream is finishing (this library's quantise / schedule kernels say when), and its first
+// statement is the wait for that kernel's completion - so launch latency overlaps the predecessor instead of following it.
+template <typename Kern>
+int launch_dependent(Kern kern, int grid, int threads, int smem_bytes, int cluster, cudaStream_t stream, const MapSet& maps,
+                     const amoe::MoeParams& p) {
+    cudaLaunchConfig_t cfg = {};
+    cfg.gridDim = dim3(static_cast<unsigned>(grid));
+    cfg.blockDim = dim3(static_cast<unsigned>(threads));
+    cfg.dynamicSmemBytes = static_cast<size_t>(smem_bytes);
+    cfg.stream = stream;
+    cudaLaunchAttribute attrs[2];
+    int n = 0;
+    attrs[n].id = cudaLaunchAttributeProgrammaticStreamSerialization;
+    attrs[n].val.programmaticStreamSerializationAllowed = 1;
+    ++n;
+    if (cluster > 1) {
+        attrs[n].id = cudaLaunchAttributeClusterDimension;
+        attrs[n].val.clusterDim.x = static_cast<unsigned>(cluster);
+        attrs[n].val.clusterDim.y = 1;
+        attrs[n].val.clusterDim.z = 1;
+        ++n;
+    }
+    cfg.attrs = attrs;
+    cfg.numAttrs = static_cast<unsigned>(n);
+    CUDA_TRY(cudaLaunchKernelEx(&cfg, kern, maps.w, maps.w2, p));
+    return ALPHA_MOE_OK;
+}
+
 template <int BMP, int SPC, int EW = (BMP >= 64 ? 2 : 1), bool PEERS = false>
 int launch_variant(const MapSet& maps, const amoe::MoeParams& p, int grid, int smem_bytes, int dev, cudaStream_t stream) {
     auto kern = amoe::fused_moe_w8a8_up_down_sm100_kernel<BMP, SPC, EW, PEERS>;
     static std::atomic<int> configured[kMaxDevices];
     if (int rc = ensure_smem_attr(kern, configured, dev)) return rc;
     constexpr int threads = 128 * EW + 128;
-    if (p.ksplit > 1) {
-        cudaLaunchConfig_t cfg = {};
-        cfg.gridDim = dim3(static_cast<unsigned>(grid));
-        cfg.blockDim = dim3(threads);
-        cfg.dynamicSmemBytes = static_cast<size_t>(smem_bytes);
-        cfg.stream = stream;
-        cudaLaunchAttribute attr;
-        attr.id = cudaLaunchAttributeClusterDimension;
-        attr.val.clusterDim.x = static_cast<unsigned>(p.ksplit);
-        attr.val.clusterDim.y = 1;
-        attr.val.clusterDim.z = 1;
-        cfg.attrs = &attr;
-        cfg.numAttrs = 1;
-        CUDA_TRY(cudaLaunchKernelEx(&cfg, kern, maps.w, maps.w2, p));
-        return ALPHA_MOE_OK;
-    }
-    kern<<<grid, threads, smem_bytes, stream>>>(maps.w, maps.w2, p);
-    CUDA_TRY(cudaGetLastError());
-    return ALPHA_MOE_OK;
+    return launch_dependent(kern, grid, threads, smem_bytes, p.ksplit, stream, maps, p);
 }
 
 template <int SPC>
@@ -198,9 +209,7 @@ int launch_tokmajor(const MapSet& maps, const amoe::MoeParams& p, int grid, int 
     auto kern = amoe::fused_moe_w8a8_up_down_sm100_tokmajor_kernel<SPC>;
     static std::atomic<int> configured[kMaxDevices];
     if (int rc = ensure_smem_attr(kern, configured, dev)) return rc;
-    kern<<<grid, amoe::kTmThreads, smem_bytes, stream>>>(maps.w, maps.w2, p);
-    CUDA_TRY(cudaGetLastError());
-    return ALPHA_MOE_OK;
+    return launch_dependent(kern, grid, amoe::kTmThreads, smem_bytes, 1, stream, maps, p);
 }
 
 // Without a device to ask: GPCs of about 18 SMs, a cluster inside one GPC, one CTA per SM.

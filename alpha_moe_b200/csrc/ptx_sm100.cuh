@@ -326,6 +326,12 @@ __device__ __forceinline__ int ld_global_nc_s32(const int* p) {
     asm volatile("ld.global.nc.s32 %0, [%1];" : "=r"(v) : "l"(p));
     return v;
 }
+// Programmatic dependent launch.  A kernel launched with the programmatic-serialisation attribute may start while
+// the kernel in front of it in the stream is still running; griddep_wait() returns once that kernel has completed and
+// its writes are visible (at once if there is no such dependency), so nothing it produced may be read before.
+// griddep_launch_dependents() tells the scheduler that the kernel behind this one may start now.
+__device__ __forceinline__ void griddep_wait() { asm volatile("griddepcontrol.wait;" ::: "memory"); }
+__device__ __forceinline__ void griddep_launch_dependents() { asm volatile("griddepcontrol.launch_dependents;" ::: "memory"); }
 __device__ __forceinline__ float bf16_round(float v) { return __bfloat162float(__float2bfloat16_rn(v)); }
 
 }  // namespace amoe

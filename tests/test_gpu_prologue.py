@@ -155,3 +155,54 @@ def test_fused_experts_single_call_matches_the_step_by_step_sequence(m, conf, tm
     fused_experts_impl(hs2, *dw, wts.cuda(), ids.cuda(), routed_scaling_factor=2.5, config=str(table))
     torch.cuda.synchronize()
     assert torch.equal(hs2.cpu(), hs.cpu()) or orc.rel_l2(hs2.cpu(), hs.cpu()) <= 1e-2   # reduction order may differ
+
+
+def test_back_to_back_layers_with_changing_inputs_eager_and_from_a_graph():
+    """The operator is launched with programmatic stream serialisation (its CTAs may be scheduled while the
+    quantise/schedule kernel in front of it is still running, and wait for that kernel's completion before reading
+    anything).  Several layers in a row, each with its own activations and routing but through the same scratch
+    memory, must each see their own schedule and activations - eagerly and replayed from one CUDA graph."""
+    from alpha_moe_b200.layer import fused_experts_impl
+    e, k, inter, top_k = 16, 1024, 256, 4
+    g = torch.Generator().manual_seed(77)
+    w, w_scale, w2, w2_scale = orc.make_weights(e, k, inter, g)
+    dw = [t.cuda() for t in (w, w_scale, w2, w2_scale)]
+    steps = []
+    for m, bm, bn, wn in ((3, 16, 32, 8), (50, 16, 32, 8), (50, 32, 64, 4), (200, 128, 64, 4), (7, 8, 32, 8)):
+        hidden = torch.randn(m, k, generator=g).to(torch.bfloat16)
+        ids, wts = orc.route_topk(torch.randn(m, e, generator=g), top_k)
+        xq, xs = orc.quant_token_groups(hidden)
+        sid, eid, npp = orc.moe_align_block_size(ids, bm, e)
+        ref = orc.fused_moe_w8a8_up_down_oracle(xq, xs, w, w_scale, w2, w2_scale, sid, eid, npp, wts, top_k, bm, 2.5)
+        conf = {"block_m": bm, "block_n": bn, "warp_n": wn, "stages": 3}
+        steps.append((hidden, ids.cuda(), wts.cuda(), conf, ref))
+
+    def run_all(bufs):
+        for (hidden, ids, wts, conf, _), hs in zip(steps, bufs):
+            fused_experts_impl(hs, *dw, wts, ids, routed_scaling_factor=2.5, config=conf)
+
+    bufs = [s[0].cuda() for s in steps]
+    run_all(bufs)
+    torch.cuda.synchronize()
+    for (_, _, _, conf, ref), hs in zip(steps, bufs):
+        assert orc.rel_l2(hs.cpu(), ref) <= 2e-2, conf
+
+    static = [s[0].cuda() for s in steps]
+    side = torch.cuda.Stream()
+    side.wait_stream(torch.cuda.current_stream())
+    with torch.cuda.stream(side):
+        run_all([b.clone() for b in static])              # warm-up on the capture stream
+    torch.cuda.current_stream().wait_stream(side)
+    torch.cuda.synchronize()
+    graph = torch.cuda.CUDAGraph()
+    with torch.cuda.graph(graph):
+        run_all(static)
+    for rep in range(2):
+        for (hidden, _, _, _, _), hs in zip(steps, static):
+            hs.copy_(hidden.cuda())
+        graph.replay()
+        torch.cuda.synchronize()
+        for (_, _, _, conf, ref), hs in zip(steps, static):
+            assert orc.rel_l2(hs.cpu(), ref) <= 2e-2, (rep, conf)
+    from alpha_moe_b200 import capi
+    assert capi.read_status(reset=True)[0] == 0
