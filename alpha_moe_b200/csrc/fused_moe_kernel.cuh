@@ -140,6 +140,7 @@ fused_moe_w8a8_up_down_sm100_kernel(const __grid_constant__ CUtensorMap tm_w,
     int pid_pre[PRE];
     int expert;
     griddep_wait();      // the schedule, the activations and the cleared `out` may come from the kernel just before
+    griddep_launch_dependents();   // an exchange kernel behind this launch may be scheduled; it waits for our completion
     {
         const int npad_raw = ld_global_nc_s32(p.num_tokens_post_padded);
         const int expert_raw = ld_global_nc_s32(p.expert_ids + mblock);

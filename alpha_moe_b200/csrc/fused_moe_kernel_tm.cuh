@@ -83,6 +83,7 @@ fused_moe_w8a8_up_down_sm100_tokmajor_kernel(const __grid_constant__ CUtensorMap
     const int mblock = blockIdx.x / ngroups;
     const int slice0 = (blockIdx.x - mblock * ngroups) * SPC;
     griddep_wait();      // the schedule, the activations and the cleared `out` may come from the kernel just before
+    griddep_launch_dependents();   // a kernel behind this launch may be scheduled; it waits for our completion
     const int npad = min(p.num_tokens_post_padded[0], p.sorted_num);
     if (mblock * p.block_m >= npad) return;
     const int expert = p.expert_ids[mblock];

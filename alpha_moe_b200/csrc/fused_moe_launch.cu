@@ -212,6 +212,23 @@ int launch_tokmajor(const MapSet& maps, const amoe::MoeParams& p, int grid, int 
     return launch_dependent(kern, grid, amoe::kTmThreads, smem_bytes, 1, stream, maps, p);
 }
 
+// Launch of one of the exchange kernels as a programmatic dependent of the kernel in front of it in the stream (its
+// first statement is griddepcontrol.wait): its CTAs may be scheduled while that kernel - normally the fused kernel,
+// which releases its dependents at entry - is still running.
+template <typename... KArgs, typename... Args>
+cudaError_t launch_after(void (*kern)(KArgs...), int blocks, int threads, cudaStream_t stream, Args... args) {
+    cudaLaunchConfig_t cfg = {};
+    cfg.gridDim = dim3(static_cast<unsigned>(blocks));
+    cfg.blockDim = dim3(static_cast<unsigned>(threads));
+    cfg.stream = stream;
+    cudaLaunchAttribute attr;
+    attr.id = cudaLaunchAttributeProgrammaticStreamSerialization;
+    attr.val.programmaticStreamSerializationAllowed = 1;
+    cfg.attrs = &attr;
+    cfg.numAttrs = 1;
+    return cudaLaunchKernelEx(&cfg, kern, static_cast<KArgs>(args)...);
+}
+
 // Without a device to ask: GPCs of about 18 SMs, a cluster inside one GPC, one CTA per SM.
 void model_cluster_capacity(int sms, int* clusters) {
     const int gpcs = sms >= 18 ? (sms + 9) / 18 : 1;
@@ -305,6 +322,7 @@ struct TpFlags {
 };
 __global__ void tp_barrier_kernel(TpFlags flags, int world, int rank, amoe::KernelStatus* status, long long limit_cycles) {
     __shared__ uint32_t epoch;
+    amoe::griddep_wait();       // launched as a programmatic dependent: the kernel in front must have completed
     uint32_t* mine = flags.of_rank[rank];
     if (threadIdx.x == 0) {
         epoch = mine[amoe::kMaxTpWorld] + 1;
@@ -345,6 +363,7 @@ __global__ void __launch_bounds__(256)
 tp_exchange_sum_kernel(TpExchange b, uint4* result, uint4* clear_next, int nvec, int nclear, int world, int rank,
                        amoe::KernelStatus* status, long long limit_cycles) {
     __shared__ int arrived;
+    amoe::griddep_wait();       // launched as a programmatic dependent: the fused kernel in front must have completed
     uint32_t* mine = b.flags[rank];
     const int t = threadIdx.x;
     const uint32_t e = *reinterpret_cast<volatile uint32_t*>(mine + amoe::kMaxTpWorld) + 1;
@@ -456,6 +475,7 @@ __device__ __forceinline__ uint4 ld_cg_v4(const uint4* p) {
 }
 __global__ void __launch_bounds__(256)
 tp_allreduce_kernel(TpExchange b, int nvec, int world, int rank, amoe::KernelStatus* status, long long limit_cycles) {
+    amoe::griddep_wait();       // launched as a programmatic dependent: the fused kernel in front must have completed
     uint32_t* mine = b.flags[rank];
     uint32_t* ticket = mine + amoe::kMaxTpWorld + 1;
     const int t = threadIdx.x;
@@ -707,8 +727,7 @@ int alpha_moe_b200_tp_barrier(void* const* flags, int tp_world, int tp_rank, int
     DeviceFacts facts;
     if (int rc = device_facts(dev, &facts)) return rc;
     const long long limit = static_cast<long long>(timeout_ms) * 2000000LL;      // about 2 GHz
-    tp_barrier_kernel<<<1, 32, 0, static_cast<cudaStream_t>(stream)>>>(f, tp_world, tp_rank, facts.status, limit);
-    CUDA_TRY(cudaGetLastError());
+    CUDA_TRY(launch_after(tp_barrier_kernel, 1, 32, static_cast<cudaStream_t>(stream), f, tp_world, tp_rank, facts.status, limit));
     return ALPHA_MOE_OK;
 }
 
@@ -742,9 +761,8 @@ int alpha_moe_b200_tp_exchange_sum(void* const* partials, void* result, void* cl
     int blocks = (std::max(nvec, nclear) + 255) / 256;
     blocks = std::max(1, std::min(blocks, facts.sms));
     const long long limit = static_cast<long long>(timeout_ms) * 2000000LL;
-    tp_exchange_sum_kernel<<<blocks, 256, 0, static_cast<cudaStream_t>(stream)>>>(
-        b, static_cast<uint4*>(result), static_cast<uint4*>(clear_next), nvec, nclear, tp_world, tp_rank, facts.status, limit);
-    CUDA_TRY(cudaGetLastError());
+    CUDA_TRY(launch_after(tp_exchange_sum_kernel, blocks, 256, static_cast<cudaStream_t>(stream), b, static_cast<uint4*>(result),
+                          static_cast<uint4*>(clear_next), nvec, nclear, tp_world, tp_rank, facts.status, limit));
     return ALPHA_MOE_OK;
 }
 
@@ -774,8 +792,7 @@ int alpha_moe_b200_tp_allreduce(void* const* bufs, long long count, void* const*
     // every CTA must be resident at once (all of them wait for the peers): at most one per SM
     const int blocks = std::max(1, std::min((per + 511) / 512, facts.sms));      // (two per SM measured the same)
     const long long limit = static_cast<long long>(timeout_ms) * 2000000LL;
-    tp_allreduce_kernel<<<blocks, 256, 0, static_cast<cudaStream_t>(stream)>>>(b, nvec, tp_world, tp_rank, facts.status, limit);
-    CUDA_TRY(cudaGetLastError());
+    CUDA_TRY(launch_after(tp_allreduce_kernel, blocks, 256, static_cast<cudaStream_t>(stream), b, nvec, tp_world, tp_rank, facts.status, limit));
     return ALPHA_MOE_OK;
 }
 
