@@ -30,6 +30,8 @@ lib.alpha_moe_b200_tp_exchange_sum.argtypes = [ctypes.POINTER(_vp), _vp, _vp, ct
                                                ctypes.POINTER(_vp), _i, _i, _i, _vp]
 lib.alpha_moe_b200_tp_allreduce.restype = _i
 lib.alpha_moe_b200_tp_allreduce.argtypes = [ctypes.POINTER(_vp), ctypes.c_longlong, ctypes.POINTER(_vp), _i, _i, _i, _vp]
+lib.alpha_moe_b200_tp_reduce_scatter.restype = _i
+lib.alpha_moe_b200_tp_reduce_scatter.argtypes = [ctypes.POINTER(_vp), ctypes.c_longlong, ctypes.POINTER(_vp), _i, _i, _i, _vp]
 lib.alpha_moe_b200_tp_barrier.restype = _i
 lib.alpha_moe_b200_tp_barrier.argtypes = [ctypes.POINTER(_vp), _i, _i, _i, _vp]
 lib.alpha_moe_b200_read_status.restype = _i
@@ -110,6 +112,14 @@ def tp_allreduce(bufs, count, flags, tp_rank, timeout_ms=1000, stream=0) -> None
     ba = (_vp * len(bufs))(*bufs)
     fa = (_vp * len(flags))(*flags)
     _check(lib.alpha_moe_b200_tp_allreduce(ba, count, fa, len(bufs), tp_rank, timeout_ms, stream))
+
+
+def tp_reduce_scatter(bufs, count, flags, tp_rank, timeout_ms=1000, stream=0) -> None:
+    """Enqueues the reduce-scatter over the ranks' peer-mapped buffers: this rank's slice of its own buffer receives
+    the sum over all ranks (device addresses; count in bf16 elements)."""
+    ba = (_vp * len(bufs))(*bufs)
+    fa = (_vp * len(flags))(*flags)
+    _check(lib.alpha_moe_b200_tp_reduce_scatter(ba, count, fa, len(bufs), tp_rank, timeout_ms, stream))
 
 
 def moe_align_block_size(topk_ids, numel, num_experts, block_m, sorted_token_ids, expert_ids,

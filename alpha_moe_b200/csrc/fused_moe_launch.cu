@@ -474,7 +474,8 @@ __device__ __forceinline__ uint4 ld_cg_v4(const uint4* p) {
     return q;
 }
 __global__ void __launch_bounds__(256)
-tp_allreduce_kernel(TpExchange b, int nvec, int world, int rank, amoe::KernelStatus* status, long long limit_cycles) {
+tp_allreduce_kernel(TpExchange b, int nvec, int world, int rank, amoe::KernelStatus* status, long long limit_cycles,
+                    int gather) {
     amoe::griddep_wait();       // launched as a programmatic dependent: the fused kernel in front must have completed
     uint32_t* mine = b.flags[rank];
     uint32_t* ticket = mine + amoe::kMaxTpWorld + 1;
@@ -535,8 +536,9 @@ tp_allreduce_kernel(TpExchange b, int nvec, int world, int rank, amoe::KernelSta
     __syncthreads();
     if (last_s) tp_signal_all(b, world, rank, e0 + 2);
     ok = tp_wait_all<1>(mine, world, e0 + 2, rank, status, limit_cycles, 100) && ok;
-    if (ok) {
-        // phase 2: the other ranks' finished slices, four vectors per thread and step
+    if (ok && gather) {
+        // phase 2 (all-reduce only; a reduce-scatter stops at the barrier above, after which no rank reads a peer's
+        // buffer any more): the other ranks' finished slices, four vectors per thread and step
         for (int q = 1; q < world; ++q) {
             const int r = (rank + q) % world;
             const int lo = r * per, hi = min(nvec, lo + per);
@@ -766,8 +768,24 @@ int alpha_moe_b200_tp_exchange_sum(void* const* partials, void* result, void* cl
     return ALPHA_MOE_OK;
 }
 
+namespace {
+int tp_reduce(void* const* bufs, long long count, void* const* flags, int tp_world, int tp_rank, int timeout_ms,
+              void* stream, int gather);
+}
+
 int alpha_moe_b200_tp_allreduce(void* const* bufs, long long count, void* const* flags, int tp_world, int tp_rank,
                                 int timeout_ms, void* stream) {
+    return tp_reduce(bufs, count, flags, tp_world, tp_rank, timeout_ms, stream, 1);
+}
+
+int alpha_moe_b200_tp_reduce_scatter(void* const* bufs, long long count, void* const* flags, int tp_world, int tp_rank,
+                                     int timeout_ms, void* stream) {
+    return tp_reduce(bufs, count, flags, tp_world, tp_rank, timeout_ms, stream, 0);
+}
+
+namespace {
+int tp_reduce(void* const* bufs, long long count, void* const* flags, int tp_world, int tp_rank, int timeout_ms,
+              void* stream, int gather) {
     if (!bufs || !flags) return fail(ALPHA_MOE_E_ARG, "null pointer argument");
     if (tp_world < 1 || tp_world > amoe::kMaxTpWorld || tp_rank < 0 || tp_rank >= tp_world)
         return fail(ALPHA_MOE_E_ARG, "tp_world must be in 1..%d and 0 <= tp_rank < tp_world (got %d, %d)",
@@ -792,9 +810,11 @@ int alpha_moe_b200_tp_allreduce(void* const* bufs, long long count, void* const*
     // every CTA must be resident at once (all of them wait for the peers): at most one per SM
     const int blocks = std::max(1, std::min((per + 511) / 512, facts.sms));      // (two per SM measured the same)
     const long long limit = static_cast<long long>(timeout_ms) * 2000000LL;
-    CUDA_TRY(launch_after(tp_allreduce_kernel, blocks, 256, static_cast<cudaStream_t>(stream), b, nvec, tp_world, tp_rank, facts.status, limit));
+    CUDA_TRY(launch_after(tp_allreduce_kernel, blocks, 256, static_cast<cudaStream_t>(stream), b, nvec, tp_world, tp_rank,
+                          facts.status, limit, gather));
     return ALPHA_MOE_OK;
 }
+}  // namespace
 
 int alpha_moe_b200_selftest_wait_timeout(int limit_cycles, int where, int iter, int32_t* result2, void* stream) {
     if (!result2) return fail(ALPHA_MOE_E_ARG, "result2 is null");

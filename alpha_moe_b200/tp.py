@@ -169,3 +169,16 @@ class PeerAllReduce:
         j, m = self._cur
         capi.tp_allreduce(self._bufs[j], m * self.hidden, self._flag_ptrs, self.rank, self.timeout_ms,
                           torch.cuda.current_stream().cuda_stream)
+
+    def reduce_scatter(self) -> torch.Tensor:
+        """Sum over all ranks of this rank's share of the rows only (alpha_moe_b200_tp_reduce_scatter): returns the
+        [rows of this rank, hidden] view of the current buffer that holds it.  The token count of the step must be a
+        multiple of the number of ranks."""
+        from . import capi
+        j, m = self._cur
+        if m % self.world != 0:
+            raise ValueError(f"{m} tokens do not split evenly over {self.world} ranks")
+        capi.tp_reduce_scatter(self._bufs[j], m * self.hidden, self._flag_ptrs, self.rank, self.timeout_ms,
+                               torch.cuda.current_stream().cuda_stream)
+        per = m // self.world
+        return self.out[j, self.rank * per:(self.rank + 1) * per]

@@ -450,7 +450,7 @@ def main():
             if ev:
                 ev[2].record()
             if ar:
-                ar.all_reduce()
+                ar.reduce_scatter() if own_exchange == "reduce_scatter" else ar.all_reduce()
             elif world > 1:
                 dist.all_reduce(out)
             if ev:
@@ -801,7 +801,7 @@ def main():
     if sampler:
         sampler.start()
     step_ms, kern_ms, inp, knobs = time_steps(wl, m, args.steps, args.warmup)
-    exchange, step_ms_nccl, step_ms_own = None, None, None
+    exchange, step_ms_nccl, step_ms_own, step_ms_rs = None, None, None, None
     if world > 1:
         # the exchange step of the headline: the NCCL all-reduce or this library's own kernel, whichever is faster here
         step_ms_nccl, exchange = step_ms, "NCCL all-reduce"
@@ -809,6 +809,8 @@ def main():
             step_ms_own, kern_own, _, _ = time_steps(wl, m, args.steps, args.warmup, own_exchange=True)
             if step_ms_own < step_ms_nccl:
                 step_ms, kern_ms, exchange = step_ms_own, kern_own, "own all-reduce kernel over peer-mapped buffers"
+            if m % world == 0:      # for a consumer that takes row shards: the first half of the exchange only (not the headline)
+                step_ms_rs = time_steps(wl, m, args.steps, args.warmup, own_exchange="reduce_scatter")[0]
     clocks = sampler.stop() if sampler else None
     e2e_ms, h2d, d2h, e2e_how = time_e2e(wl, m, args.steps, args.warmup)
     parity = tp_parity(wl, m, own_exchange=(exchange is not None and exchange.startswith("own"))) if world > 1 else None
@@ -914,7 +916,10 @@ def main():
         }
         if parity is not None:
             line["tp_parity_rel_l2"], line["tp_parity_vs_oracle"] = round(parity[0], 5), round(parity[1], 5)
-            line["exchange"] = {"used": exchange, "ms_per_step_nccl": step_ms_nccl, "ms_per_step_own_allreduce": step_ms_own}
+            line["exchange"] = {"used": exchange, "ms_per_step_nccl": step_ms_nccl, "ms_per_step_own_allreduce": step_ms_own,
+                                "ms_per_step_own_reduce_scatter": step_ms_rs,
+                                "reduce_scatter_note": "same step with the exchange stopped after every rank has summed its own "
+                                                       "rows (a consumer that takes row shards); not the headline"}
             if own_notes:
                 line["exchange"]["unavailable"] = own_notes
         if cpu:

@@ -97,6 +97,16 @@ int alpha_moe_b200_tp_exchange_sum(void* const* partials, void* result, void* cl
 int alpha_moe_b200_tp_allreduce(void* const* bufs, long long count, void* const* flags, int tp_world, int tp_rank,
                                 int timeout_ms, void* stream);
 
+/* The first half of the all-reduce above for callers whose next operator takes row shards (sequence-parallel layers):
+ * same arguments, same flag protocol and barriers, but the kernel stops after every rank has summed ITS slice, so each
+ * rank reads (tp_world-1)/tp_world of the payload over NVLink instead of twice that.  On return bufs[tp_rank] holds
+ * the sum over all ranks in elements [tp_rank * per, min(count, (tp_rank + 1) * per)), per = 8 * ceil(count / 8 /
+ * tp_world) (whole rows when the token count is a multiple of tp_world and the row length of 8); the rest of the
+ * buffer holds this rank's partial values.  No rank reads a peer's buffer after the kernel's closing barrier, so a
+ * buffer may be cleared and reused as soon as the call has completed in stream order. */
+int alpha_moe_b200_tp_reduce_scatter(void* const* bufs, long long count, void* const* flags, int tp_world, int tp_rank,
+                                     int timeout_ms, void* stream);
+
 /* Replaces the external moe_align_block_size the reference calls before the operator
  * (jit_moe.py:158, extra/sglang.patch:33-35).  topk_ids [numel] i32 (the flattened [M,top_k] expert
  * ids; ids outside [0,num_experts) are ignored).  Outputs: sorted_token_ids

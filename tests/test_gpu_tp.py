@@ -165,6 +165,28 @@ def _worker_allreduce(rank, world, port, result_path):
         if rank == 0:
             results[step] = {"rel_sum": orc.rel_l2(got, part.cpu()), "got": got, "case": case, "bm": bm}
         dist.barrier()      # the cross-GPU waits are bounded (1 s): no rank may run ahead while another does host work
+    # the reduce-scatter form: every rank ends up with the summed rows of its own share only
+    for step, (m, bm, bn, wn, st) in enumerate(((300, 128, 64, 4, 3), (34, 16, 32, 8, 3))):
+        case = orc.make_case(16, 1024, 512, m, 5, seed=300 + m, shared=True, scaling=2.5, weights=weights)
+        sid, eid, npp = [t.to(dev) for t in case.schedule(bm)]
+        x, xs, wts = case.x.to(dev), case.x_scale.to(dev), case.topk_weights.to(dev)
+        out = ar.next_buffer(m)
+        torch.ops.alpha_moe.fused_moe_w8a8_up_down(x, xs, *shard, sid, eid, npp, wts, out, case.top_k, bm, bn, wn, st, 2.5)
+        part = out.float().clone()
+        mine = ar.reduce_scatter()
+        torch.cuda.synchronize()
+        assert capi.read_status(reset=True)[0] == 0
+        assert mine.shape == (m // world, 1024)
+        dist.all_reduce(part)
+        per = m // world
+        rel_sum = orc.rel_l2(mine.cpu(), part[rank * per:(rank + 1) * per].cpu())
+        rows = [torch.empty_like(mine) for _ in range(world)]
+        dist.all_gather(rows, mine.contiguous())
+        worst = torch.tensor([rel_sum], device=dev)
+        dist.all_reduce(worst, op=dist.ReduceOp.MAX)
+        if rank == 0:
+            results[f"rs{step}"] = {"rel_sum": float(worst), "got": torch.cat(rows).cpu(), "case": case, "bm": bm}
+        dist.barrier()
     if rank == 0:
         # the CPU oracle takes seconds: only after the last step, when no rank is waiting in a kernel
         for v in results.values():
@@ -178,11 +200,12 @@ def _worker_allreduce(rank, world, port, result_path):
 def test_tp2_own_all_reduce_over_peer_mapped_buffers(tmp_path):
     """alpha_moe_b200_tp_allreduce (slice sums + slice fetches over NVLink, two flag barriers) after the operator:
     against the fp32 sum of the ranks' partial outputs (only the bf16 rounding of the sum may differ) and the oracle;
-    every rank must hold identical bits.  Three steps of different sizes over the two alternating buffers."""
+    every rank must hold identical bits.  Three steps of different sizes over the two alternating buffers, then two
+    steps with alpha_moe_b200_tp_reduce_scatter, whose row shards put together must give the same layer output."""
     import torch.multiprocessing as mp
     result = str(tmp_path / "ra.pt")
     mp.spawn(_worker_allreduce, args=(2, _free_port(), result), nprocs=2, join=True)
     r = torch.load(result)
-    assert len(r) == 3
+    assert len(r) == 5 and "rs0" in r and "rs1" in r      # three all-reduce steps, two reduce-scatter steps
     for step, v in r.items():
         assert v["rel_sum"] <= 5e-3 and v["rel_oracle"] <= 2e-2, (step, v)

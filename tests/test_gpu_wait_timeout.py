@@ -40,7 +40,7 @@ def test_selftest_rejects_limits_that_would_stall_the_gpu():
         capi.selftest_wait_timeout(10000, 1, 1, 0)
 
 
-@pytest.mark.parametrize("which", ["barrier", "exchange_sum", "allreduce"])
+@pytest.mark.parametrize("which", ["barrier", "exchange_sum", "allreduce", "reduce_scatter"])
 def test_cross_gpu_wait_runs_out_when_a_rank_never_arrives(which):
     """The tensor-parallel exchange kernels wait for the other ranks through flag words in peer-mapped memory.  Here
     "rank 1" is a flag array that nothing ever writes (one GPU, no second process): rank 0's wait must run out after
@@ -60,8 +60,10 @@ def test_cross_gpu_wait_runs_out_when_a_rank_never_arrives(which):
         capi.tp_barrier(fp, 0, 5, st)
     elif which == "exchange_sum":
         capi.tp_exchange_sum(bp, result.data_ptr(), 0, n, 0, fp, 0, 5, st)
-    else:
+    elif which == "allreduce":
         capi.tp_allreduce(bp, n, fp, 0, 5, st)
+    else:
+        capi.tp_reduce_scatter(bp, n, fp, 0, 5, st)
     t1.record()
     torch.cuda.synchronize()
     assert 2.0 < t0.elapsed_time(t1) < 200.0            # about the 5 ms limit (twice for the two-phase all-reduce)
@@ -70,4 +72,4 @@ def test_cross_gpu_wait_runs_out_when_a_rank_never_arrives(which):
     if which == "exchange_sum":
         assert (result == 7.0).all()                     # not written after a run-out wait
     # rank 0 did announce itself to "rank 1": once, and once more for the all-reduce's second phase
-    assert int(flags[1][0]) == (2 if which == "allreduce" else 1)
+    assert int(flags[1][0]) == (2 if which in ("allreduce", "reduce_scatter") else 1)
