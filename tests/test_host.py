@@ -225,3 +225,21 @@ def test_tensor_parallel_entry_points_reject_bad_arguments_before_any_launch():
     for bufs, count, msg in (([p, p], 12, "multiple of 8"), ([p, p + 8], 64, "misaligned"), ([p] * 9, 64, "tp_world")):
         with pytest.raises(capi.AlphaMoeError, match=msg):
             capi.tp_allreduce(bufs, count, [p] * len(bufs), 0)
+        with pytest.raises(capi.AlphaMoeError, match=msg):
+            capi.tp_reduce_scatter(bufs, count, [p] * len(bufs), 0)
+
+
+def test_quant_and_align_entry_rejects_bad_arguments_before_any_launch():
+    """alpha_moe_b200_quant_and_align (both steps in front of the operator in one call): argument errors come back as
+    error codes from both of its forms - one launch (M * top_k <= 1024) and two launches - without touching a GPU."""
+    from alpha_moe_b200 import capi
+    p = 0x10000
+    base = dict(x_bf16=p, x_fp8=p, x_scale=p, M=4, K=512, zero_src=1, topk_ids=p, top_k=2, num_experts=8, block_m=16,
+                sorted_token_ids=p, expert_ids=p, num_tokens_post_padded=p)
+    for bad, msg in ((dict(M=0), "positive"), (dict(top_k=0), "positive"), (dict(x_fp8=0), "null"), (dict(topk_ids=0), "null"),
+                     (dict(K=500), "multiple of 128"), (dict(x_bf16=p + 8), "aligned"), (dict(num_experts=5000), "num_experts"),
+                     (dict(block_m=0), "block_m"),
+                     (dict(M=4096, x_scale=0), "null"), (dict(M=4096, K=100), "multiple of 128"),
+                     (dict(M=4096, x_bf16=p + 8), "aligned")):
+        with pytest.raises(capi.AlphaMoeError, match=msg):
+            capi.quant_and_align(*dict(base, **bad).values())
