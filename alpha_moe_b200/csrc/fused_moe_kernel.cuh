@@ -74,7 +74,7 @@ __device__ __forceinline__ void red_out_all_ranks(const MoeParams& p, size_t off
 // landed, UMMAs issued, completion seen by the epilogue, read-back, buffer handed back - takes well over a thousand
 // cycles while its UMMAs need about a hundred at these widths, so a narrow tile keeps as many chunks in flight as
 // fit 256 columns (two CTAs of that size can share an SM's 512).
-__host__ __device__ constexpr int acc_buffers(int bmp) { return bmp <= 16 ? 8 : bmp == 32 ? 4 : 2; }
+__host__ __device__ constexpr int acc_buffers(int bmp, int ew = 1) { return bmp <= 16 ? 8 : bmp == 32 ? 4 : (bmp == 64 && ew == 2) ? 4 : 2; }
 
 struct SmemPlan {
     uint32_t stage_bytes, hq, xs, swg, swu, sw2, tokrow, topkw, tokscale, amax, part, bars, misc, total;
@@ -97,7 +97,7 @@ __host__ __device__ inline SmemPlan smem_plan(int bmp, int s, int kc, int spc, i
     p.tokscale = o;  o += spc * bmp * 4;
     p.amax = o;      o += bmp * 8;
     p.part = o;      o += ksplit > 1 ? 2 * bmp * 128 * 4 : 0;
-    p.bars = o;      o += (2 * s + 2 * acc_buffers(bmp) + 6) * 8;
+    p.bars = o;      o += (2 * s + 2 * acc_buffers(bmp, 2) + 6) * 8;      // (room for the wider of the two 64-token shapes)
     p.misc = o;      o += 16;
     p.total = o;
     return p;
@@ -115,7 +115,7 @@ fused_moe_w8a8_up_down_sm100_kernel(const __grid_constant__ CUtensorMap tm_w,
     constexpr int NC = BMP / NEPI_WG;
     constexpr int EPI_THREADS = 128 * NEPI_WG;
     constexpr int W_G0 = 4 * NEPI_WG, W_MMA0 = W_G0 + 2;   // control warpgroup: gather, gather, UMMA, UMMA
-    constexpr int NB = acc_buffers(BMP);         // accumulator buffers (chunks in flight between UMMA and epilogue)
+    constexpr int NB = acc_buffers(BMP, EW);     // accumulator buffers (chunks in flight between UMMA and epilogue)
     constexpr uint32_t TMEM_COLS = NB * 2 * BMP; // buffers x two accumulators x BMP columns
     static_assert(BMP == 16 || BMP == 32 || BMP == 64 || BMP == 128, "padded block_m");
     static_assert(SPC == 1 || SPC == 2, "slices per CTA");
