@@ -174,41 +174,56 @@ moe_align_chunks_kernel(const int32_t* ids, int numel, int E, int block, int32_t
 }
 
 // Everything in one CTA when there is a single chunk (numel <= kChunk: e.g. up to 113 tokens at top_k = 9).
-// cnt: 8 * kMaxExperts ints, start: kMaxExperts + 1 ints of shared memory.
+// cnt: 8 * kMaxExperts ints, warp_tot: 8 ints of shared memory.  Thread t owns the experts [t * per, (t + 1) * per):
+// their padded sizes, then (after a scan over the threads: warp shuffles and the eight warp totals) their first output
+// slots - a single thread walking over all experts took longer than everything else in this kernel together.
 __device__ __forceinline__ void align_single_body(const int32_t* ids, int numel, int E, int block, int32_t* sorted,
                                                   int sorted_len, int32_t* expert_ids, int n_blocks_max,
-                                                  int32_t* num_post_pad, int* cnt, int* start) {
+                                                  int32_t* num_post_pad, int* cnt, int* warp_tot) {
     for (int i = threadIdx.x; i < sorted_len; i += kAlignThreads) sorted[i] = numel;
     for (int i = threadIdx.x; i < n_blocks_max; i += kAlignThreads) expert_ids[i] = 0;
-    count_chunk(ids, numel, 0, E, cnt);
-    for (int e = threadIdx.x; e < E; e += kAlignThreads) {
-        int s = 0;
+    count_chunk(ids, numel, 0, E, cnt);                   // (its barriers also order the default fills before the writes below)
+    const int per = (E + kAlignThreads - 1) / kAlignThreads;           // <= 4
+    int padded[4], mine = 0;
 #pragma unroll
-        for (int w = 0; w < 8; ++w) s += cnt[w * E + e];
-        start[e] = (s + block - 1) / block * block;            // padded size for now
+    for (int i = 0; i < 4; ++i) {
+        const int e = threadIdx.x * per + i;
+        padded[i] = 0;
+        if (i < per && e < E) {
+            int tot = 0;
+#pragma unroll
+            for (int w = 0; w < 8; ++w) tot += cnt[w * E + e];
+            padded[i] = (tot + block - 1) / block * block;
+            mine += padded[i];
+        }
     }
+    const int lane = threadIdx.x & 31, warp = threadIdx.x >> 5;
+    int incl = mine;
+#pragma unroll
+    for (int d = 1; d < 32; d <<= 1) {
+        const int v = __shfl_up_sync(0xFFFFFFFFu, incl, d);
+        if (lane >= d) incl += v;
+    }
+    if (lane == 31) warp_tot[warp] = incl;
     __syncthreads();
-    if (threadIdx.x == 0) {
-        int run = 0;
-        for (int e = 0; e < E; ++e) {
-            const int n = start[e];
-            start[e] = run;
-            run += n;
-        }
-        start[E] = run;
-        num_post_pad[0] = run;
-    }
-    __syncthreads();                                            // also orders the default fills above before the writes below
-    for (int e = threadIdx.x; e < E; e += kAlignThreads) {
-        int run = start[e];
+    int run = incl - mine;
+    for (int w = 0; w < warp; ++w) run += warp_tot[w];
 #pragma unroll
-        for (int w = 0; w < 8; ++w) {
-            const int n = cnt[w * E + e];
-            cnt[w * E + e] = run;
-            run += n;
+    for (int i = 0; i < 4; ++i) {
+        const int e = threadIdx.x * per + i;
+        if (i < per && e < E) {
+            for (int b = run / block; b < (run + padded[i]) / block; ++b) expert_ids[b] = e;
+            int slot = run;
+#pragma unroll
+            for (int w = 0; w < 8; ++w) {          // counts -> first slot of each warp's assignments of expert e
+                const int n = cnt[w * E + e];
+                cnt[w * E + e] = slot;
+                slot += n;
+            }
+            run += padded[i];
         }
-        for (int b = start[e] / block; b < start[e + 1] / block; ++b) expert_ids[b] = e;
     }
+    if (threadIdx.x == kAlignThreads - 1) num_post_pad[0] = run;       // the last thread's running end = total
     __syncthreads();
     scatter_chunk(ids, numel, 0, E, cnt, sorted);
 }
@@ -217,9 +232,9 @@ __global__ void __launch_bounds__(kAlignThreads)
 moe_align_single_kernel(const int32_t* ids, int numel, int E, int block, int32_t* sorted, int sorted_len,
                         int32_t* expert_ids, int n_blocks_max, int32_t* num_post_pad) {
     __shared__ int cnt[8 * kMaxExperts];
-    __shared__ int start[kMaxExperts + 1];
+    __shared__ int warp_tot[kAlignThreads / 32];
     launch_dependents();
-    align_single_body(ids, numel, E, block, sorted, sorted_len, expert_ids, n_blocks_max, num_post_pad, cnt, start);
+    align_single_body(ids, numel, E, block, sorted, sorted_len, expert_ids, n_blocks_max, num_post_pad, cnt, warp_tot);
 }
 
 // ------------------------------------------------------------------------------------------------
@@ -322,11 +337,11 @@ quant_and_align_small_kernel(__nv_bfloat16* x, uint8_t* q, float* scale, long lo
                              const int32_t* ids, int numel, int E, int block, int32_t* sorted, int sorted_len,
                              int32_t* expert_ids, int n_blocks_max, int32_t* num_post_pad) {
     __shared__ int cnt[8 * kMaxExperts];
-    __shared__ int start[kMaxExperts + 1];
+    __shared__ int warp_tot[kAlignThreads / 32];
     static_assert(kAlignThreads == 256, "one block shape for both halves");
     launch_dependents();      // the operator behind this launch may be scheduled; it waits for our completion
     if (blockIdx.x == gridDim.x - 1) {
-        align_single_body(ids, numel, E, block, sorted, sorted_len, expert_ids, n_blocks_max, num_post_pad, cnt, start);
+        align_single_body(ids, numel, E, block, sorted, sorted_len, expert_ids, n_blocks_max, num_post_pad, cnt, warp_tot);
         return;
     }
     group_quant_body(x, q, scale, n_groups, zero_src, blockIdx.x, gridDim.x - 1);
