@@ -122,11 +122,16 @@ int get_maps(int device, const void* w, const void* w2, int E, int N, int K, Map
 constexpr int kMaxKsplit = 8;        // portable cluster size limit
 
 // Facts about a device that never change, looked up once: the SM count, the address of the status word and how many
-// clusters of 2..8 CTAs of the small-batch kernel (one CTA per SM) the device can hold at the same time.
+// clusters of 2..8 CTAs of the small-batch kernel the device can hold at the same time - with one CTA per SM (deep
+// ring) and with two (a ring shallow enough for two CTAs to share an SM's shared memory).
+struct ClusterCapacity {
+    int one_per_sm[kMaxKsplit + 1] = {};
+    int two_per_sm[kMaxKsplit + 1] = {};
+};
 struct DeviceFacts {
     int sms = 0;
     amoe::KernelStatus* status = nullptr;
-    int clusters[kMaxKsplit + 1] = {};
+    ClusterCapacity clusters;
 };
 constexpr int kMaxDevices = 64;
 
@@ -230,12 +235,24 @@ cudaError_t launch_after(void (*kern)(KArgs...), int blocks, int threads, cudaSt
 }
 
 // Without a device to ask: GPCs of about 18 SMs, a cluster inside one GPC, one CTA per SM.
-void model_cluster_capacity(int sms, int* clusters) {
+// With two CTAs per SM a cluster of an even size fills half as many SMs, and two clusters of an odd size share the
+// SMs of one.  (The occupancy calculator cannot be asked: it reports one CTA of these kernels per SM whatever the ring
+// size, although two do run side by side; the figures below match what was measured - e.g. 58 units at the DeepSeek
+// shard shape with a two-slot ring: clusters of 4 fit (48 us), clusters of 5 do not (60 us).)
+void two_per_sm_from_one(ClusterCapacity* c) {
+    c->two_per_sm[0] = 0;
+    c->two_per_sm[1] = 2 * c->one_per_sm[1];
+    for (int ks = 2; ks <= kMaxKsplit; ++ks)
+        c->two_per_sm[ks] = ks % 2 == 0 ? c->one_per_sm[ks / 2] : 2 * c->one_per_sm[ks];
+}
+
+void model_cluster_capacity(int sms, ClusterCapacity* c) {
     const int gpcs = sms >= 18 ? (sms + 9) / 18 : 1;
     const int per_gpc = sms / gpcs;
-    clusters[0] = 0;
-    clusters[1] = sms;
-    for (int ks = 2; ks <= kMaxKsplit; ++ks) clusters[ks] = gpcs * (per_gpc / ks);
+    c->one_per_sm[0] = 0;
+    c->one_per_sm[1] = sms;
+    for (int ks = 2; ks <= kMaxKsplit; ++ks) c->one_per_sm[ks] = gpcs * (per_gpc / ks);
+    two_per_sm_from_one(c);
 }
 
 int device_facts(int dev, DeviceFacts* out) {
@@ -246,17 +263,17 @@ int device_facts(int dev, DeviceFacts* out) {
     DeviceFacts& f = dev < kMaxDevices ? facts[dev] : local;
     if (!f.status) {
         CUDA_TRY(cudaDeviceGetAttribute(&f.sms, cudaDevAttrMultiProcessorCount, dev));
-        model_cluster_capacity(f.sms, f.clusters);
+        model_cluster_capacity(f.sms, &f.clusters);
         // The driver knows how the SMs are grouped (a cluster lives inside one GPC): ask it, keep the model's figure
-        // where it does not answer.  Asked for the narrow weight-major shape with a ring that leaves room for one
-        // CTA per SM, which is what the small-batch launches use.
+        // where it does not answer.  Asked for the narrow weight-major shape with a ring that leaves room for one CTA
+        // per SM; the figures for two per SM follow from those.
         auto kern = amoe::fused_moe_w8a8_up_down_sm100_kernel<16, 1>;
         if (cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, kMaxDynSmem) == cudaSuccess) {
-            for (int ks = 2; ks <= kMaxKsplit; ++ks) {
+            auto ask = [&](int ks, int smem_bytes, int* into) {
                 cudaLaunchConfig_t cfg = {};
                 cfg.gridDim = dim3(static_cast<unsigned>(ks * 64));
                 cfg.blockDim = dim3(256);
-                cfg.dynamicSmemBytes = static_cast<size_t>(kPairDynSmem + 1024);
+                cfg.dynamicSmemBytes = static_cast<size_t>(smem_bytes);
                 cudaLaunchAttribute attr;
                 attr.id = cudaLaunchAttributeClusterDimension;
                 attr.val.clusterDim.x = static_cast<unsigned>(ks);
@@ -265,9 +282,11 @@ int device_facts(int dev, DeviceFacts* out) {
                 cfg.attrs = &attr;
                 cfg.numAttrs = 1;
                 int n = 0;
-                if (cudaOccupancyMaxActiveClusters(&n, kern, &cfg) == cudaSuccess && n > 0) f.clusters[ks] = n;
-            }
+                if (cudaOccupancyMaxActiveClusters(&n, kern, &cfg) == cudaSuccess && n > 0) *into = n;
+            };
+            for (int ks = 2; ks <= kMaxKsplit; ++ks) ask(ks, kPairDynSmem + 1024, &f.clusters.one_per_sm[ks]);
         }
+        two_per_sm_from_one(&f.clusters);
         (void)cudaGetLastError();
         CUDA_TRY(cudaGetSymbolAddress(reinterpret_cast<void**>(&f.status), g_status));
     }
@@ -299,16 +318,22 @@ __global__ void wait_selftest_kernel(amoe::KernelStatus* status, int* result, lo
 std::atomic<int> g_ksplit_override{0};     // 0 = automatic; set through alpha_moe_b200_set_ksplit (tuners, tests)
 
 // Clusters of CTAs along K for small batches (narrow tile, one slice per CTA only): the largest cluster size for
-// which every (block, slice) unit of the launch still gets its cluster at once.  clusters[ks] = how many clusters of
-// ks CTAs the device holds at the same time; a launch with more units than that runs in two rounds and loses more
-// than the split gains (34 units at the DeepSeek shard shape: clusters of 3 34 us, of 4 49 us).
-int choose_ksplit(int block_m, int spc, long long nblocks, int N, int K, const int* clusters) {
+// which every (block, slice) unit of the launch still gets its cluster at once.  The capacity tables say how many
+// clusters of ks CTAs the device holds at the same time - with the ring the plan arrives at for that ks, which decides
+// whether one or two CTAs fit an SM; a launch with more units than that runs in two rounds and loses more than the
+// split gains (34 units at the DeepSeek shard shape: clusters of 3 34 us, of 4 49 us).
+int choose_ksplit(int block_m, int spc, long long nblocks, int N, int K, int stages, const ClusterCapacity& cap) {
     if (block_m > 32 || spc != 1) return 1;
     const long long units = nblocks * (N / 256);
     const int v = g_ksplit_override.load(std::memory_order_relaxed);
     if (v >= 1 && v <= kMaxKsplit && v <= K / 128) return v;
-    for (int ks = kMaxKsplit; ks >= 2; --ks)
-        if (ks <= K / 128 && units <= clusters[ks]) return ks;
+    for (int ks = kMaxKsplit; ks >= 2; --ks) {
+        if (ks > K / 128) continue;
+        int depth, bmp, smem_bytes;
+        if (plan(K, block_m, stages, spc, ks, &depth, &bmp, &smem_bytes)) continue;
+        const int fit = smem_bytes <= kPairDynSmem - 8192 ? cap.two_per_sm[ks] : cap.one_per_sm[ks];
+        if (units <= fit) return ks;
+    }
     return 1;
 }
 
@@ -612,7 +637,7 @@ int launch_fused(const void* x, const float* x_scale, const void* w, const float
     // Live blocks never exceed the number of assignments, so no more CTAs than that are launched.
     long long nblocks = (static_cast<long long>(sorted_num) + block_m - 1) / block_m;
     if (nblocks > static_cast<long long>(M) * top_k) nblocks = static_cast<long long>(M) * top_k;
-    const int ksplit = choose_ksplit(block_m, spc, nblocks, N, K, facts.clusters);
+    const int ksplit = choose_ksplit(block_m, spc, nblocks, N, K, stages, facts.clusters);
     int depth, bmp, smem_bytes;
     if (int rc = plan(K, block_m, stages, spc, ksplit, &depth, &bmp, &smem_bytes)) return rc;
 
@@ -862,17 +887,17 @@ int alpha_moe_b200_plan(int K, int N, int block_m, int block_n, int stages, int 
     if (stages < 1 || stages > 5) return fail(ALPHA_MOE_E_ARG, "stages must be in 1..5, got %d", stages);
     if (num_blocks <= 0 || num_sms < 0) return fail(ALPHA_MOE_E_ARG, "num_blocks must be positive, num_sms >= 0");
     const int spc = (block_n == 64 && (N / 256) % 2 == 0) ? 2 : 1;
-    int clusters[kMaxKsplit + 1];
+    ClusterCapacity clusters;
     if (num_sms == 0) {           // the current device, as a launch would see it
         int dev = 0;
         CUDA_TRY(cudaGetDevice(&dev));
         DeviceFacts facts;
         if (int rc = device_facts(dev, &facts)) return rc;
-        for (int i = 0; i <= kMaxKsplit; ++i) clusters[i] = facts.clusters[i];
+        clusters = facts.clusters;
     } else {
-        model_cluster_capacity(num_sms, clusters);
+        model_cluster_capacity(num_sms, &clusters);
     }
-    const int ksplit = choose_ksplit(block_m, spc, num_blocks, N, K, clusters);
+    const int ksplit = choose_ksplit(block_m, spc, num_blocks, N, K, stages, clusters);
     int depth, bmp, smem_bytes;
     if (int rc = plan(K, block_m, stages, spc, ksplit, &depth, &bmp, &smem_bytes)) return rc;
     out6[0] = depth;

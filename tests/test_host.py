@@ -125,6 +125,10 @@ def test_plan_fits_shared_memory_for_every_knob():
     for nblocks, want in ((1, 8), (8, 8), (9, 6), (12, 6), (13, 4), (16, 4), (17, 3), (24, 3), (25, 2), (36, 2), (37, 1)):
         assert capi.plan(7168, 16, 5, 32, N=512, num_blocks=nblocks)[4] == want, nblocks
     assert capi.plan(256, 16, 5, 32, N=512, num_blocks=1)[4] == 2       # never more CTAs than K chunks
+    # a ring shallow enough for two CTAs per SM doubles the room: clusters of an even size fill half as many SMs
+    for nblocks, want in ((9, 8), (16, 8), (17, 6), (24, 6), (29, 4), (36, 4), (37, 3), (48, 3), (49, 2), (74, 2), (75, 1)):
+        depth, _, smem, _, ks, _ = capi.plan(7168, 16, 2, 32, N=512, num_blocks=nblocks)
+        assert ks == want and depth == 2 and smem <= 105 * 1024, nblocks
     with pytest.raises(capi.AlphaMoeError):
         capi.set_ksplit(9)
 
