@@ -186,8 +186,8 @@ int alpha_moe_b200_selftest_wait_timeout(int limit_cycles, int where, int iter, 
 /* What the launcher uses for a problem and a knob tuple; for tuners and tests.  It runs the launcher's own
  * planning code.  num_blocks = live upper bound of schedule blocks, min(ceil(sorted_num / block_m), M * top_k);
  * num_sms = SM count of a device (148 on B200): the cluster capacity that decides ksplit is then modelled (GPCs of
- * about 18 SMs, one CTA per SM) and nothing touches a device; num_sms = 0 = the current device, whose driver is asked
- * as a launch would (launches nothing).  out6 = {ring_depth, padded_block_m, dynamic_smem_bytes,
+ * about 18 SMs; one CTA per SM, two when the ring is shallow enough for two to share an SM) and nothing touches a
+ * device; num_sms = 0 = the current device, whose driver is asked as a launch would (launches nothing).  out6 = {ring_depth, padded_block_m, dynamic_smem_bytes,
  * slices_per_cta (2 when block_n = 64 and N/256 is even), ksplit (CTAs per cluster along K, small batches: the
  * largest of 2..8 for which all (block, slice) units get their cluster at the same time, else 1),
  * kernel (0 weight-major, 1 token-major)}. */
