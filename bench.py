@@ -14,6 +14,7 @@ Beside the headline the JSON line carries sub-records for the rest of the metric
            the step replayed from a CUDA graph)
   qwen3    the Qwen3-Next TP2 shard (E=512, K=2048, I=256, top_k=10) over M      (1 GPU only)
   zipf     the headline shape at M=8192 with Zipf(1.2) routing                   (1 GPU only)
+  imbalance  the headline shape at M=256 and 4096 under the reference script's balancedness levels 0.8 ... 0.5 (1 GPU only)
   tp_fixed the unsharded layer I=2048 split I/N per GPU ("strong" scaling) at M = 1, 64, 1024, 8192
   layer    the whole call-site sequence from bf16 activations and topk_ids (quantise + clear + schedule
            + operator, one C-ABI call) over M
@@ -153,6 +154,20 @@ def route_zipf(m, n_routed, k_routed, s, gen, shared_expert):
     return ids.contiguous(), wts.float().contiguous()
 
 
+def route_mixture(m, n_routed, k_routed, balancedness, gen, shared_expert):
+    """The imbalance model of the reference's timing script (test/test_moe_performance.py:42-49): every routed
+    assignment is drawn independently - so an expert may repeat inside a token - from balancedness x uniform +
+    (1 - balancedness) x "always expert 0"."""
+    p = torch.full((n_routed,), balancedness / n_routed, dtype=torch.float32)
+    p[0] += 1.0 - balancedness
+    ids = torch.multinomial(p, m * k_routed, replacement=True, generator=gen).view(m, k_routed).to(torch.int32)
+    wts = torch.softmax(torch.randn(m, k_routed, generator=gen), -1)
+    if shared_expert is not None:
+        ids = torch.cat([ids, torch.full((m, 1), shared_expert, dtype=torch.int32)], 1)
+        wts = torch.cat([wts, torch.ones(m, 1)], 1)
+    return ids.contiguous(), wts.float().contiguous()
+
+
 def align_block_size(topk_ids: torch.Tensor, block: int, num_experts: int):
     """Input generator for the benchmark: block schedule with the layout moe_align_block_size
     produces (each expert's assignments padded with the sentinel M*top_k to a multiple of block)."""
@@ -195,7 +210,9 @@ class Workload:
         n_routed = sh.e - 1 if sh.shared else sh.e
         k_routed = sh.top_k - 1 if sh.shared else sh.top_k
         shared = sh.e - 1 if sh.shared else None
-        if zipf is None:
+        if isinstance(zipf, tuple):        # ("balancedness", b): the reference script's imbalance model
+            ids, wts = route_mixture(m, n_routed, k_routed, zipf[1], torch.Generator().manual_seed(2), shared)
+        elif zipf is None:
             ids, wts = route(torch.randn(m, n_routed, generator=gc), k_routed, shared)
         else:
             # the law covers the first 240 routed experts: the other 16 receive nothing (empty experts in the schedule)
@@ -823,7 +840,7 @@ def main():
         achieved, peak, unit = f["flops"] / (kern_ms * 1e-3) / 1e12, fp8_peak, "TFLOP/s"
     tr = traffic.get(("deepseek", m))
 
-    sweep, qwen, zipf, tp_fixed, layer = [], [], None, [], []
+    sweep, qwen, zipf, tp_fixed, layer, imbalance = [], [], None, [], [], []
     if not args.no_sweep:
         for ms_ in SWEEP_MS:
             s_ms, k_ms, sinp, sk = time_steps(wl, ms_, 10, 3)
@@ -852,6 +869,14 @@ def main():
             zipf = sweep_record(sh, 8192, s_ms, k_ms, sinp, sk,
                                 {"routing": "Zipf(1.2) over 240 of the 256 routed experts, seed 1",
                                  "empty_experts": int((counts == 0).sum()), "max_share_of_tokens": round(float(counts.max()) / 8192, 3)})
+            # the reference's own imbalance levels (its timing script sweeps balancedness 0.8 ... 0.5 at every M)
+            for ms_ in (256, 4096):
+                for bal in (0.8, 0.7, 0.6, 0.5):
+                    s_ms, k_ms, sinp, sk = time_steps(wl, ms_, 5, 3, zipf=("balancedness", bal))
+                    counts = torch.bincount(sinp["ids"].reshape(-1).long(), minlength=sh.e)[:-1]
+                    imbalance.append(sweep_record(sh, ms_, s_ms, k_ms, sinp, sk,
+                                                  {"balancedness": bal,
+                                                   "share_of_routed_assignments_on_expert_0": round(float(counts[0]) / float(counts.sum()), 3)}))
             wq = Workload(QWEN3, dev, rank)
             for ms_ in QWEN_MS:
                 s_ms, k_ms, sinp, sk = time_steps(wq, ms_, 6, 3)
@@ -911,7 +936,7 @@ def main():
                     "h2d_bytes_per_step": h2d, "d2h_bytes_per_step": d2h, "rows": e2e_how,
                     "pipeline": "copy-in / layer / copy-out of consecutive steps on three streams, two buffer sets"},
             "gpu_launches": launches[0], "host_us_per_call_m1": host_us,
-            "clocks": clocks, "kernel_status": list(status), "sweep": sweep, "layer": layer, "zipf": zipf,
+            "clocks": clocks, "kernel_status": list(status), "sweep": sweep, "layer": layer, "zipf": zipf, "imbalance": imbalance,
             "qwen3": qwen, "tp_fixed": tp_fixed,
         }
         if parity is not None:
