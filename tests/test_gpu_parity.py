@@ -304,3 +304,18 @@ def test_operator_replays_from_a_cuda_graph(m, bm, bn, wn, st):
         g.replay()
         torch.cuda.synchronize()
         assert orc.rel_l2(out.cpu(), eager.cpu()) <= 1e-2
+
+
+@pytest.mark.parametrize("balancedness", [0.8, 0.5])
+def test_reference_timing_scripts_imbalance_model(balancedness):
+    """Routing of the reference's timing script (test/test_moe_performance.py:42-49): every routed assignment drawn
+    independently from balancedness x uniform + (1 - balancedness) x expert 0 - one hot expert that owns dozens of
+    blocks, duplicates inside a token, experts that receive nothing - through every kernel shape."""
+    import bench
+    e, k, inter, m, top_k = 24, 1024, 256, 300, 6
+    base = orc.make_case(e, k, inter, m, top_k, seed=31, shared=True, scaling=2.5)
+    ids, wts = bench.route_mixture(m, e - 1, top_k - 1, balancedness, torch.Generator().manual_seed(5), e - 1)
+    case = dataclasses.replace(base, topk_ids=ids, topk_weights=wts)
+    assert float((ids[:, :-1] == 0).float().mean()) > (1 - balancedness) * 0.8        # expert 0 is hot
+    for bm, bn, wn, st in ((8, 64, 4, 3), (16, 32, 8, 5), (32, 64, 4, 2), (64, 64, 4, 2), (64, 32, 8, 4), (128, 64, 4, 3)):
+        check_close(run_capi(case, bm, bn, wn, st), orc.run_oracle(case, bm), tag=f"mixture {balancedness} bm={bm} bn={bn}")
