@@ -451,6 +451,8 @@ def main():
             own_ar[hidden] = make_on_all_ranks("own_allreduce", lambda: PeerAllReduce(max(SWEEP_MS), hidden, timeout_ms=2000))
         return own_ar[hidden]
 
+    last_median = [0.0]
+
     def time_steps(wl, m, steps, warmup, zipf=None, own_exchange=False):
         """(ms per whole step, ms per fused-kernel launch) as the max over ranks, inputs, knobs.  The exchange step at
         N > 1 is the NCCL all-reduce, or with own_exchange this library's all-reduce kernel over peer-mapped buffers."""
@@ -481,9 +483,11 @@ def main():
             one(ev[i])
         barrier()
         launches[0] += steps
-        step_ms = sum(e[0].elapsed_time(e[3]) for e in ev) / steps
+        per_step = sorted(e[0].elapsed_time(e[3]) for e in ev)
+        step_ms = sum(per_step) / steps
         kern_ms = sum(e[1].elapsed_time(e[2]) for e in ev) / steps
-        step_ms, kern_ms = max_over_ranks(step_ms, kern_ms)
+        step_ms, kern_ms, med = max_over_ranks(step_ms, kern_ms, per_step[steps // 2])
+        last_median[0] = med                         # one late host thread on one rank moves the mean of ten steps a lot
         return step_ms, kern_ms, inp, knobs
 
     def host_us_per_call(wl, m, calls=300):
@@ -553,7 +557,7 @@ def main():
         for i in range(4):
             graphs[i & 1].replay()
         barrier()
-        tot = 0.0
+        ts = []
         for i in range(2 * steps):
             flush.fill_(i & 0xFF)
             barrier()
@@ -562,10 +566,11 @@ def main():
             graphs[i & 1].replay()
             e1.record()
             torch.cuda.synchronize()
-            tot += e0.elapsed_time(e1)
+            ts.append(e0.elapsed_time(e1))
         launches[0] += 2 * steps
         del graphs, g                                # before any communicator is torn down
-        (ms,) = max_over_ranks(tot / (2 * steps))
+        ts.sort()
+        (ms,) = max_over_ranks(ts[len(ts) // 2])     # median: the ranks are re-aligned on the host before every replay
         return ms
 
     def time_fused_tp(wl, m, steps, warmup):
@@ -844,7 +849,7 @@ def main():
     if not args.no_sweep:
         for ms_ in SWEEP_MS:
             s_ms, k_ms, sinp, sk = time_steps(wl, ms_, 10, 3)
-            extra = {}
+            extra = {"us_step_median": round(last_median[0] * 1e3, 1)}
             if ms_ <= GRAPH_MAX_M:
                 extra["us_step_graph"] = round(time_graph_step(wl, ms_, 10) * 1e3, 1)
             if world > 1 and ms_ >= 256:
