@@ -354,6 +354,30 @@ static __device__ __align__(256) int g_align_scratch[kNoAllocScratchInts];
 
 }  // namespace amoe_aux
 
+// A second stream and two events per (host thread, device) for entry points that run two independent kernels side by
+// side: fork from the caller's stream, join back into it.  Created at the first use (make that first call outside
+// any stream capture) and kept for the life of the thread.
+struct SideStream {
+    cudaStream_t stream = nullptr;
+    cudaEvent_t fork = nullptr, join = nullptr;
+    bool ready = false;
+};
+static SideStream* side_stream(int dev) {
+    thread_local SideStream per_device[64];
+    if (dev < 0 || dev >= 64) return nullptr;
+    SideStream& s = per_device[dev];
+    if (!s.ready) {
+        if (cudaStreamCreateWithFlags(&s.stream, cudaStreamNonBlocking) != cudaSuccess ||
+            cudaEventCreateWithFlags(&s.fork, cudaEventDisableTiming) != cudaSuccess ||
+            cudaEventCreateWithFlags(&s.join, cudaEventDisableTiming) != cudaSuccess) {
+            (void)cudaGetLastError();
+            return nullptr;              // the caller falls back to one stream
+        }
+        s.ready = true;
+    }
+    return &s;
+}
+
 extern "C" {
 
 int64_t alpha_moe_b200_align_workspace_bytes(int numel, int num_experts) {
@@ -477,11 +501,7 @@ int alpha_moe_b200_quant_and_align(void* x_bf16, void* x_fp8, float* x_scale, in
     if (M <= 0 || top_k <= 0) return fail(ALPHA_MOE_E_ARG, "M and top_k must be positive");
     const long long numel = static_cast<long long>(M) * top_k;
     if (numel > 0x7FFFFFFFLL) return fail(ALPHA_MOE_E_ARG, "M*top_k overflows int32");
-    if (numel > kChunk) {        // two launches: the schedule needs several CTAs and a grid-wide barrier
-        if (int rc = alpha_moe_b200_per_token_group_quant_fp8(x_bf16, x_fp8, x_scale, M, K, zero_src, stream)) return rc;
-        return alpha_moe_b200_moe_align_block_size(topk_ids, static_cast<int>(numel), num_experts, block_m,
-                                                   sorted_token_ids, expert_ids, num_tokens_post_padded, workspace, stream);
-    }
+    // every argument is checked before anything touches a device or a stream
     if (!x_bf16 || !x_fp8 || !x_scale || !topk_ids || !sorted_token_ids || !expert_ids || !num_tokens_post_padded)
         return fail(ALPHA_MOE_E_ARG, "null pointer argument");
     if (K <= 0 || K % 128 != 0) return fail(ALPHA_MOE_E_ARG, "need M > 0 and K a positive multiple of 128");
@@ -490,6 +510,27 @@ int alpha_moe_b200_quant_and_align(void* x_bf16, void* x_fp8, float* x_scale, in
     if (num_experts <= 0 || num_experts > kMaxExperts)
         return fail(ALPHA_MOE_E_ARG, "num_experts must be in 1..%d (got %d)", kMaxExperts, num_experts);
     if (block_m <= 0) return fail(ALPHA_MOE_E_ARG, "block_m must be positive (got %d)", block_m);
+    if (numel > kChunk) {
+        // Two launches (the schedule needs several CTAs and a grid-wide barrier) that do not depend on each other: the
+        // schedule runs on a side stream forked from the caller's and joined back into it, beside the quantiser.  It
+        // is launched first so that its few CTAs have their places before the quantiser's grid fills every SM.
+        cudaStream_t user = static_cast<cudaStream_t>(stream);
+        int dev = 0;
+        AUX_TRY(cudaGetDevice(&dev));
+        SideStream* side = side_stream(dev);
+        const bool forked = side && cudaEventRecord(side->fork, user) == cudaSuccess &&
+                            cudaStreamWaitEvent(side->stream, side->fork, 0) == cudaSuccess;
+        const int rc_align = alpha_moe_b200_moe_align_block_size(topk_ids, static_cast<int>(numel), num_experts, block_m,
+                                                                 sorted_token_ids, expert_ids, num_tokens_post_padded,
+                                                                 workspace, forked ? side->stream : user);
+        const int rc_quant = rc_align ? rc_align
+                                      : alpha_moe_b200_per_token_group_quant_fp8(x_bf16, x_fp8, x_scale, M, K, zero_src, stream);
+        if (forked) {            // joined whatever happened above: the side stream never stays attached to a capture
+            AUX_TRY(cudaEventRecord(side->join, side->stream));
+            AUX_TRY(cudaStreamWaitEvent(user, side->join, 0));
+        }
+        return rc_quant;
+    }
     const long long sorted_len = numel + static_cast<long long>(num_experts) * (block_m - 1);
     if (sorted_len > 0x7FFFFFFFLL) return fail(ALPHA_MOE_E_ARG, "schedule too long for int32 indices");
     const int n_blocks_max = static_cast<int>((sorted_len + block_m - 1) / block_m);

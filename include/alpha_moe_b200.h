@@ -146,7 +146,10 @@ int alpha_moe_b200_per_token_group_quant_fp8(void* x_bf16, void* x_fp8, float* x
 /* The two steps in front of the operator at the reference's call sites - the quantisation above (jit_moe.py:142,
  * extra/sglang.patch:30-31) and the block schedule (jit_moe.py:158, extra/sglang.patch:33-35) - are independent of
  * each other.  This entry runs both: as ONE launch when the schedule fits one CTA (M * top_k <= 1024: decode-size
- * batches, where a launch costs about as much as either step), otherwise as the two launches above.  Outputs are
+ * batches, where a launch costs about as much as either step), otherwise as the two launches above side by side - the
+ * schedule on a stream of the library's own that is forked from `stream` and joined back into it before the call
+ * returns (capturable; one such stream and two events per host thread and device, created at the first use: make that
+ * first call outside any stream capture).  Outputs are
  * bit-identical to alpha_moe_b200_per_token_group_quant_fp8 + alpha_moe_b200_moe_align_block_size with the same
  * arguments (numel = M * top_k; workspace as for that entry, unused for M * top_k <= 1024). */
 int alpha_moe_b200_quant_and_align(void* x_bf16, void* x_fp8, float* x_scale, int M, int K, int zero_src,
