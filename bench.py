@@ -601,6 +601,63 @@ def main():
         (ms,) = max_over_ranks(tot / steps)
         return ms
 
+    def time_fused_tp_train(wl, m, per_graph=8, replays=5):
+        """The own-exchange step as a decode loop sees it: eight steps in ONE graph, the L2 overwritten between them
+        inside the graph.  Only the first step of a replay absorbs the ranks' launch skew; from then on the exchange
+        itself keeps the ranks together, as it does layer after layer in a model.  Per step = (the graph's time - the
+        time of a graph that holds the eight L2 overwrites alone) / 8; medians over the replays, max over ranks.
+        None if the peer-memory layer is unavailable or anything in here fails (on every rank alike)."""
+        lay = fused_tp.get("layer")
+        if lay is None:
+            return None
+        sh = wl.shape
+        inp, d, _, _, (bm, bn, wn, st) = prepare(wl, m)
+
+        def one():
+            lay.run(inp["x"], inp["x_scale"], wl.w, wl.w_scale, wl.w2, wl.w2_scale, d["sid"], d["eid"], d["npp"],
+                    d["topk_weights"], sh.top_k, bm, bn, wn, st, sh.scaling)
+
+        def build():
+            s = torch.cuda.Stream()
+            s.wait_stream(torch.cuda.current_stream())
+            g_steps, g_flush = torch.cuda.CUDAGraph(), torch.cuda.CUDAGraph()
+            with torch.cuda.stream(s):
+                one()
+                one()
+                torch.cuda.synchronize()
+                with torch.cuda.graph(g_steps, stream=s):
+                    for k in range(per_graph):
+                        flush.fill_(k)
+                        one()
+                with torch.cuda.graph(g_flush, stream=s):
+                    for k in range(per_graph):
+                        flush.fill_(k)
+            torch.cuda.current_stream().wait_stream(s)
+            return g_steps, g_flush
+        graphs = make_on_all_ranks("own_exchange_train", build)
+        if graphs is None:
+            return None
+        g_steps, g_flush = graphs
+
+        def med(g):
+            ts = []
+            for _ in range(replays):
+                barrier()
+                e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+                e0.record()
+                g.replay()
+                e1.record()
+                torch.cuda.synchronize()
+                ts.append(e0.elapsed_time(e1))
+            ts.sort()
+            return ts[len(ts) // 2]
+        med(g_steps)                                 # warm-up replays
+        t_steps, t_flush = med(g_steps), med(g_flush)
+        launches[0] += 2 * per_graph * replays
+        del graphs, g_steps, g_flush
+        (ms,) = max_over_ranks((t_steps - t_flush) / per_graph)
+        return ms
+
     def time_layer(wl, m, steps, warmup):
         """The call-site sequence as one C-ABI call (alpha_moe_b200_fused_experts): bf16 activations and topk_ids in,
         layer output in the same buffer: group quantisation + clearing + block schedule + fused operator."""
@@ -860,6 +917,9 @@ def main():
                 if t_own is not None:
                     extra["us_step_own_exchange"] = round(t_own * 1e3, 1)
                     extra["us_step_own_exchange_graph"] = round(time_graph_step(wl, ms_, 10, own_exchange=True) * 1e3, 1)
+                    t_train = time_fused_tp_train(wl, ms_)
+                    if t_train is not None:
+                        extra["us_step_own_exchange_graph8"] = round(t_train * 1e3, 1)
             sweep.append(sweep_record(sh, ms_, s_ms, k_ms, sinp, sk, extra))
         for ms_ in LAYER_MS:
             if world == 1:
